@@ -8,10 +8,12 @@ import torch
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values per token: n_kv heads of head_dim.  `window` (or None)
-    is how many of the latest positions the mixer ever reads."""
+    is how many of the latest positions the mixer ever reads.  `v_head_dim`
+    (or None: head_dim) is the values' head size where it differs from the keys'."""
     n_kv: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)

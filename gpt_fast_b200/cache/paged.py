@@ -38,7 +38,7 @@ class _KVGroup:
         self.index = {e: i for i, e in enumerate(entries)}
         shape = (len(entries), n_pages, need.n_kv, page_size, need.head_dim)
         self.k_pool = torch.zeros(shape, dtype=dtype, device=device)
-        self.v_pool = torch.zeros(shape, dtype=dtype, device=device)
+        self.v_pool = torch.zeros(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
         self.pages = FreeList(n_pages, "page")
         self.table_host = torch.full((n_slots, max_pages), -1, dtype=torch.int32)
         self.table = self.table_host.to(device)
@@ -173,8 +173,9 @@ class Cache:
         return min((g.pages.n_free for g in self.kv_groups), default=self.n_pages)
 
     def bytes(self) -> int:
-        n = sum(g.k_pool.numel() * g.k_pool.element_size() * 2 for g in self.kv_groups)
+        n = sum((g.k_pool.numel() + g.v_pool.numel()) * g.k_pool.element_size() for g in self.kv_groups)
         return n + sum(g.data.numel() * g.data.element_size() for g in self.state_groups)
 
     def kv_bytes_per_token(self) -> int:
-        return sum(2 * len(g.entries) * g.need.n_kv * g.need.head_dim * g.k_pool.element_size() for g in self.kv_groups)
+        return sum(len(g.entries) * g.need.n_kv * (g.need.head_dim + (g.need.v_head_dim or g.need.head_dim)) * g.k_pool.element_size()
+                   for g in self.kv_groups)

@@ -53,6 +53,8 @@ def architecture_for(cfg: Dict[str, Any]) -> Architecture:
     if cfg.get("model_type"):
         keys.append(cfg["model_type"])
     keys += list(cfg.get("architectures") or [])
+    if isinstance(cfg.get("architecture"), str):
+        keys.append(cfg["architecture"])
     for k in keys:
         if k in _ARCHITECTURES:
             return _ARCHITECTURES[k]

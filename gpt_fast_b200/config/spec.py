@@ -29,6 +29,7 @@ class LayerSpec:
     block: str
     parts: Dict[str, PartSpec]
     position: Optional[PartSpec] = None   # position encoding the layer's mixers apply
+    block_params: Dict[str, Any] = field(default_factory=dict)   # constants of the arrangement itself (a factor on its branches, ...)
 
 
 @dataclass(frozen=True)

@@ -5,7 +5,11 @@
 // whole cache with a boolean mask (model.py:209-211): query head h reads
 // key/value head h / (H/G); the key at position j is visible to the query at
 // position p iff j <= p (and p - j < window when a window is set); scores are
-// scaled by `scale`; softmax is 32-bit.
+// scaled by `scale`; softmax is 32-bit.  Options that other mixers use: `chunk` (a query
+// sees only keys of its own block of `chunk` positions, blocks counted from
+// position 0 of the sequence), `sink` (one number per query head whose
+// exponential joins the softmax denominator without a value) and a value head
+// size `dv` of its own.
 //
 // One block per (token, query head).  Keys are visited in chunks of 128 that
 // start at multiples of 128 of the ABSOLUTE position, with an online softmax
@@ -23,7 +27,8 @@ constexpr int MAX_DPT = 4;      // head_dim <= CHUNK * MAX_DPT
 template <typename T>
 __global__ void __launch_bounds__(CHUNK)
 attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedKV kv, GfbBatch b,
-                         int H, int G, int d, float scale, int window, int* status) {
+                         int H, int G, int d, int dv, float scale, int window, int chunk,
+                         const float* __restrict__ sink, int* status) {
     extern __shared__ float smem[];
     float* qs = smem;              // [d]
     float* ps = smem + d;          // [CHUNK]
@@ -42,9 +47,10 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedK
 
     int lo = 0;
     if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
+    if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
     const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
-    const size_t head_off = (size_t)g * kv.page_size * d;
-    const size_t page_stride = (size_t)G * kv.page_size * d;
+    const size_t head_off = (size_t)g * kv.page_size * d, v_head_off = (size_t)g * kv.page_size * dv;
+    const size_t page_stride = (size_t)G * kv.page_size * d, v_page_stride = (size_t)G * kv.page_size * dv;
 
     float m_run = -INFINITY, l_run = 0.f;
     float acc[MAX_DPT];
@@ -85,25 +91,34 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedK
 #pragma unroll
         for (int r = 0; r < MAX_DPT; r++) {
             int dim = threadIdx.x + r * CHUNK;
-            if (dim < d) {
+            if (dim < dv) {
                 float a = acc[r] * corr;
                 for (int jj = 0; jj < nkeys; jj++) {
                     int pg = page_of[jj];
                     if (pg < 0) continue;
-                    const T* vrow = (const T*)kv.v_pool + (size_t)pg * page_stride + head_off
-                                    + (size_t)((c0 + jj) % kv.page_size) * d;
+                    const T* vrow = (const T*)kv.v_pool + (size_t)pg * v_page_stride + v_head_off
+                                    + (size_t)((c0 + jj) % kv.page_size) * dv;
                     a = fmaf(ps[jj], gfb_to_f32(vrow[dim]), a);
                 }
                 acc[r] = a;
             }
         }
     }
+    if (sink != nullptr) {
+        // one more term in the denominator, exp(sink_h), with no value behind it
+        const float sk = sink[h];
+        const float m_fin = fmaxf(m_run, sk);
+        const float corr = (m_run == -INFINITY) ? 0.f : expf(m_run - m_fin);
+        l_run = l_run * corr + expf(sk - m_fin);
+#pragma unroll
+        for (int r = 0; r < MAX_DPT; r++) acc[r] *= corr;
+    }
     float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-    T* orow = out + ((size_t)t * H + h) * d;
+    T* orow = out + ((size_t)t * H + h) * dv;
 #pragma unroll
     for (int r = 0; r < MAX_DPT; r++) {
         int dim = threadIdx.x + r * CHUNK;
-        if (dim < d) orow[dim] = gfb_from_f32<T>(acc[r] * inv);
+        if (dim < dv) orow[dim] = gfb_from_f32<T>(acc[r] * inv);
     }
 }
 
@@ -111,10 +126,11 @@ GFB_API int gfb_attention_generic(const void* q, void* out, int dt,
                                   void* k_pool, void* v_pool, const int* page_table, int max_pages, int page_size,
                                   int n_pages,
                                   const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths,
-                                  int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
-                                  int* status, cudaStream_t stream) {
+                                  int n_seqs, int n_tokens, int H, int G, int d, int dv, float scale, int window,
+                                  int chunk, const float* sink, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (d > CHUNK * MAX_DPT) return gfb_fail("gfb_attention_generic: head_dim %d exceeds %d", d, CHUNK * MAX_DPT);
+    if (dv <= 0) dv = d;
+    if (dv > CHUNK * MAX_DPT) return gfb_fail("gfb_attention_generic: value head size %d exceeds %d", dv, CHUNK * MAX_DPT);
     if (G <= 0 || H % G) return gfb_fail("gfb_attention_generic: %d heads do not divide into %d groups", H, G);
     if (H > 65535) return gfb_fail("gfb_attention_generic: %d heads exceed the grid limit", H);
     GfbPagedKV kv{k_pool, v_pool, page_table, max_pages, page_size, n_pages};
@@ -124,10 +140,10 @@ GFB_API int gfb_attention_generic(const void* q, void* out, int dt,
     cudaError_t e;
     if (dt == GFB_BF16)
         e = gfb_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(CHUNK), smem, stream,
-                       (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b, H, G, d, scale, window, status);
+                       (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b, H, G, d, dv, scale, window, chunk, sink, status);
     else if (dt == GFB_F32)
         e = gfb_launch(attention_generic_kernel<float>, grid, dim3(CHUNK), smem, stream,
-                       (const float*)q, (float*)out, kv, b, H, G, d, scale, window, status);
+                       (const float*)q, (float*)out, kv, b, H, G, d, dv, scale, window, chunk, sink, status);
     else
         return gfb_fail("gfb_attention_generic: unknown type %d", dt);
     return gfb_check(e, "gfb_attention_generic");

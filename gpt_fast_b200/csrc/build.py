@@ -31,6 +31,10 @@ LIBRARIES = {
     "gemm_tc": (["gemm_tc.cu"], [], []),
     "attention_bf16": (["attention_bf16.cu"], [], []),
     "attention_tc": (["attention_tc.cu"], [], []),
+    "layernorm": (["layernorm.cu"], [], []),
+    "qkv_prepare": (["qkv_prepare.cu"], [], []),
+    "retention": (["retention.cu"], [], []),
+    "elementwise": (["elementwise.cu"], [], []),
 }
 HEADERS = ["common.cuh", "attn_decode_noalloc.h"]
 

@@ -9,12 +9,21 @@
 // not depend on which other rows are in the batch.
 //
 // Epilogues: STORE (C = acc, cast), ADD (C is 32-bit, C += acc: the residual
-// sum), SWIGLU (W's rows alternate gate, up; C[M, N/2] = silu(gate) * up).
+// sum), SWIGLU (W's rows alternate gate, up; C[M, N/2] = silu(gate) * up), and
+// the unary activations GELU (exact, with erf), GELU_TANH and SILU (C = f(acc)).
 #include "common.cuh"
 
 GFB_DEFINE_LAST_ERROR()
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_GELU = 4, EPI_GELU_TANH = 5, EPI_SILU = 6 };   // 3: the tensor-core kernel's partial sums
+
+template <int EPI>
+__device__ __forceinline__ float unary(float z) {
+    if (EPI == EPI_GELU) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+    if (EPI == EPI_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    if (EPI == EPI_SILU) return z / (1.0f + expf(-z));
+    return z;
+}
 
 constexpr int BM = 64, BN = 64, BK = 16;
 
@@ -81,7 +90,7 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restr
                 if (n >= N) continue;
                 size_t o = (size_t)m * N + n;
                 if (EPI == EPI_ADD) C[o] = gfb_from_f32<TC>(gfb_to_f32(C[o]) + acc[i][j]);
-                else C[o] = gfb_from_f32<TC>(acc[i][j]);
+                else C[o] = gfb_from_f32<TC>(unary<EPI>(acc[i][j]));
             }
         }
     }
@@ -96,6 +105,9 @@ static int launch(const void* A, const void* W, void* C, int M, int N, int K, in
     if (epi == EPI_STORE) GO(EPI_STORE);
     else if (epi == EPI_ADD) GO(EPI_ADD);
     else if (epi == EPI_SWIGLU) GO(EPI_SWIGLU);
+    else if (epi == EPI_GELU) GO(EPI_GELU);
+    else if (epi == EPI_GELU_TANH) GO(EPI_GELU_TANH);
+    else if (epi == EPI_SILU) GO(EPI_SILU);
     else return gfb_fail("gfb_gemm_simt: unknown epilogue %d", epi);
 #undef GO
     return gfb_check(e, "gfb_gemm_simt");

@@ -105,10 +105,54 @@ def rmsnorm(x, weight, eps: float, out, rows=None, pending=None):
     return kernels().rmsnorm(x, weight, eps, out, rows, pending)
 
 
+def layernorm(x, weight, bias, eps: float, out, rows=None, branch=None, rms: bool = False):
+    """Layer norm with weight and bias, (v - mean) / sqrt(mean((v - mean)^2) + eps) * weight + bias, statistics in
+    32-bit.  x float32 [T, D]; out [R, D] in the compute type, or None; rows int32 [R] or None.
+    branch = (y, weight, bias, eps, mult), only without rows: the kernel first completes
+    x += mult * norm(y) with that norm's parameters (written back), y being a float32 [T, D] tensor or partial sums
+    [S, T, D] of it, and then norms the new x into `out` (if given).  rms=True: the root-mean-square form, no mean
+    and no bias, for both norms."""
+    return kernels().layernorm(x, weight, bias, eps, out, rows, branch, rms)
+
+
+def qkv_prepare(src, partials, offsets, q_out, kv: PagedKV, batch: BatchMeta, n_head: int, n_kv: int, head_dim: int,
+                v_head_dim: int, table=None, rot_dims: int = 0, pairing: str = "half", q_norm=None, k_norm=None,
+                norm_eps: float = 0.0, k_scale: float = 1.0, append: bool = True):
+    """From a projection's row to attention's inputs.  src [T, W] holds q (H heads of head_dim), k (G heads of
+    head_dim) and v (G heads of v_head_dim) at the column offsets `offsets` = (q, k, v); with `partials` (float32
+    [S, T, W]) src is their sum.  Per head, in this order: root-mean-square norm of q and k with the weights
+    q_norm / k_norm [head_dim] (None: none), rotation of the first rot_dims dimensions by the token's position from
+    `table` (None: none), k times k_scale.  q goes to q_out [T, H, head_dim], k and v to the token's place in the
+    cache (unless append is False)."""
+    return kernels().qkv_prepare(src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table,
+                                 rot_dims, pairing, q_norm, k_norm, norm_eps, k_scale, append)
+
+
+def retention(src, offsets, state, out, batch: BatchMeta, n_head: int, head_dim: int, v_head_dim: int, decay, table=None,
+              rot_dims: int = 0, pairing: str = "half", k_scale: float = 1.0):
+    """Retention over the tokens of a step: per head S = decay * S + k v^T, o = S^T q, token after token, with q and k
+    rotated on their first rot_dims dimensions and k times k_scale.  src [T, W] holds q, k (H heads of head_dim) and v
+    (H heads of v_head_dim) at the column offsets `offsets`; state float32 [n_slots, H, head_dim, v_head_dim] is the
+    sequences' carried S (read and written at the batch's slots); decay float32 [H]; out float32 [T, H, v_head_dim]."""
+    return kernels().retention(src, offsets, state, out, batch, n_head, head_dim, v_head_dim, decay, table, rot_dims, pairing, k_scale)
+
+
+def retention_gate(o, src, gate_offset: int, out, n_head: int, v_head_dim: int, eps: float):
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]) with the gate at column
+    gate_offset of src [T, W]; o float32 [T, H, dv]; out [T, H*dv] in the compute type."""
+    return kernels().retention_gate(o, src, gate_offset, out, n_head, v_head_dim, eps)
+
+
+def activation(x, kind: str, out=None):
+    """out (default: in place) = f(x) with f 'gelu' (exact, erf), 'gelu_tanh' or 'silu'."""
+    return kernels().activation(x, kind, out)
+
+
 def linear(a, w, out, mode: str = "store", defer: bool = False):
     """a [M, K] times w [N, K] transposed.  mode 'store': out [M, N] = product;
     'add': out float32 [M, N] += product (the residual sum, in 32-bit);
-    'swiglu': w's rows alternate gate, up and out [M, N/2] = silu(gate) * up.
+    'swiglu': w's rows alternate gate, up and out [M, N/2] = silu(gate) * up;
+    'gelu' (exact, erf), 'gelu_tanh', 'silu': out [M, N] = f(product).
 
     defer=True (modes 'store' and 'add'): if the kernel splits the sum over K it
     may return the partial sums (float32 [S, M, N]) INSTEAD of finishing `out`;
@@ -138,10 +182,14 @@ def rope_append(qkv, q_out, kv: PagedKV, batch: BatchMeta, table, n_head: int, n
 
 
 def attention(q, kv: PagedKV, batch: BatchMeta, out, n_head: int, n_kv: int, head_dim: int, scale: float,
-              window: Optional[int] = None):
+              window: Optional[int] = None, chunk: Optional[int] = None, sink=None, v_head_dim: Optional[int] = None):
     """Causal grouped-query attention of q [T, H, d] over the cache (which
-    already holds this step's keys and values); out [T, H*d]."""
-    return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window)
+    already holds this step's keys and values); out [T, H*dv].  chunk: a query sees only the keys of its own block
+    of `chunk` positions (counted from the sequence's first position).  sink (float32 [H]): exp(sink_h) joins the
+    softmax denominator of head h, with no value.  v_head_dim: the values' head size if it differs from d."""
+    if chunk is None and sink is None and v_head_dim in (None, head_dim):
+        return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window)
+    return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk, sink, v_head_dim or head_dim)
 
 
 def rope_append_attention(qkv, partials, kv: PagedKV, batch: BatchMeta, table, out, n_head: int, n_kv: int, head_dim: int,

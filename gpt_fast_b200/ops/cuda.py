@@ -10,7 +10,8 @@ from ..csrc import build
 from .types import BatchMeta, PagedKV
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
-_EPI = {"store": 0, "add": 1, "swiglu": 2}
+_EPI = {"store": 0, "add": 1, "swiglu": 2, "gelu": 4, "gelu_tanh": 5, "silu": 6}
+_UNARY = ("gelu", "gelu_tanh", "silu")
 _PAIRING = {"interleaved": 0, "half": 1}
 
 
@@ -186,6 +187,121 @@ class CudaKernels:
         _need(y, shape=out.shape, name="addend")
         self._call("core", "gfb_add_into", _ptr(out), _ptr(y), c_int(_dt(y)), c_long(out.numel()), _stream())
 
+    # -- layer norm, q/k/v preparation, retention, activations ---------------------------
+    def layernorm(self, x, weight, bias, eps, out, rows=None, branch=None, rms=False):
+        T, D = x.shape
+        _need(x, torch.float32, name="norm input")
+        if out is not None:
+            R = out.shape[0]
+            _need(weight, shape=(D,), name="norm weight")
+            if not rms:
+                _need(bias, weight.dtype, (D,), "norm bias")
+            _need(out, shape=(R, D), name="norm output")
+            if rows is not None:
+                _need(rows, torch.int32, (R,), "rows")
+            elif R != T:
+                _fail(f"norm output has {R} rows, input {T}")
+        else:
+            R = T
+        y = pw = pb = None
+        S, peps, mult = 0, 0.0, 0.0
+        if branch is not None:
+            y, pw, pb, peps, mult = branch
+            if rows is not None:
+                _fail("a branch sum cannot be combined with a row gather")
+            _need(pw, shape=(D,), name="branch norm weight")
+            if not rms:
+                _need(pb, pw.dtype, (D,), "branch norm bias")
+            if y.dim() == 3:
+                S = y.shape[0]
+                _need(y, torch.float32, (S, T, D), "partial sums of the branch")
+            else:
+                _need(y, torch.float32, (T, D), "branch")
+        elif out is None:
+            return
+        self._call("layernorm", "gfb_layernorm", _ptr(x), _ptr(y), c_int(S), c_long(T * D), _ptr(pw), _ptr(pb),
+                   c_int(_dt(pw) if pw is not None else 0), c_float(peps), c_float(mult), _ptr(weight if out is not None else None),
+                   _ptr(bias if out is not None else None), c_int(_dt(weight) if out is not None else 0), c_float(eps),
+                   _ptr(out), c_int(_dt(out) if out is not None else 0), _ptr(rows), c_int(R), c_int(D), c_int(1 if rms else 0),
+                   _stream())
+
+    def qkv_prepare(self, src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table=None, rot_dims=0,
+                    pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True):
+        T = batch.n_tokens
+        if partials is not None:
+            W = partials.shape[2]
+            _need(partials, torch.float32, (partials.shape[0], T, W), "partial sums of the projection")
+            source, n_part = partials, partials.shape[0]
+        else:
+            W = src.shape[1]
+            _need(src, q_out.dtype, (T, W), "projection")
+            source, n_part = src, 0
+        q_off, k_off, v_off = offsets
+        if max(q_off + n_head * head_dim, k_off + n_kv * head_dim, v_off + n_kv * v_head_dim) > W:
+            _fail(f"q, k and v at {offsets} do not fit rows of {W}")
+        _need(q_out, shape=(T, n_head, head_dim), name="q_out")
+        if table is not None:
+            _need(table, torch.float32, name="rotary table")
+            if table.shape[1] * 2 != rot_dims:
+                _fail(f"the rotary table serves {table.shape[1] * 2} dimensions, the mixer rotates {rot_dims}")
+        w_dt = 0
+        for wn in (q_norm, k_norm):
+            if wn is not None:
+                _need(wn, shape=(head_dim,), name="q/k norm weight")
+                w_dt = _dt(wn)
+        if q_norm is not None and k_norm is not None and q_norm.dtype != k_norm.dtype:
+            _fail("the q and k norm weights must have one type")
+        if append:
+            _need(kv.k_pool, q_out.dtype, name="key pool")
+            if tuple(kv.k_pool.shape[1:]) != (n_kv, kv.page_size, head_dim) or tuple(kv.v_pool.shape[1:]) != (n_kv, kv.page_size, v_head_dim):
+                _fail(f"cache pages are {tuple(kv.k_pool.shape[1:])} / {tuple(kv.v_pool.shape[1:])}, the layer needs "
+                      f"{(n_kv, kv.page_size, head_dim)} / {(n_kv, kv.page_size, v_head_dim)}")
+        self._call("qkv_prepare", "gfb_qkv_prepare", _ptr(source), c_int(n_part), c_int(W), c_int(q_off), c_int(k_off), c_int(v_off),
+                   _ptr(q_out), c_int(_dt(q_out)), *self._kv_args(kv), *self._batch_args(batch), _ptr(table),
+                   c_int(table.shape[0] if table is not None else 0), c_int(rot_dims if table is not None else 0),
+                   c_int(_PAIRING[pairing]), _ptr(q_norm), _ptr(k_norm), c_int(w_dt), c_float(norm_eps), c_float(k_scale),
+                   c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(v_head_dim), c_int(1 if append else 0), _ptr(batch.status),
+                   _stream())
+
+    def retention(self, src, offsets, state, out, batch, n_head, head_dim, v_head_dim, decay, table=None, rot_dims=0,
+                  pairing="half", k_scale=1.0):
+        T = batch.n_tokens
+        W = src.shape[1]
+        _need(src, shape=(T, W), name="projection")
+        q_off, k_off, v_off = offsets
+        if max(q_off + n_head * head_dim, k_off + n_head * head_dim, v_off + n_head * v_head_dim) > W:
+            _fail(f"q, k and v at {offsets} do not fit rows of {W}")
+        _need(state, torch.float32, (state.shape[0], n_head, head_dim, v_head_dim), "retention state")
+        _need(out, torch.float32, (T, n_head, v_head_dim), "retention output")
+        _need(decay, torch.float32, (n_head,), "decay")
+        if table is not None:
+            _need(table, torch.float32, name="rotary table")
+            if table.shape[1] * 2 != rot_dims:
+                _fail(f"the rotary table serves {table.shape[1] * 2} dimensions, the mixer rotates {rot_dims}")
+        self._call("retention", "gfb_retention", _ptr(src), c_int(_dt(src)), c_int(W), c_int(q_off), c_int(k_off), c_int(v_off),
+                   _ptr(state), _ptr(out), *self._batch_args(batch), c_int(int(batch.max_q_len)), _ptr(table),
+                   c_int(table.shape[0] if table is not None else 0), c_int(rot_dims if table is not None else 0),
+                   c_int(_PAIRING[pairing]), _ptr(decay), c_float(k_scale), c_int(n_head), c_int(head_dim), c_int(v_head_dim),
+                   _ptr(batch.status), _stream())
+
+    def retention_gate(self, o, src, gate_offset, out, n_head, v_head_dim, eps):
+        T, W = src.shape
+        _need(o, torch.float32, (T, n_head, v_head_dim), "retention output")
+        _need(src, name="projection")
+        _need(out, src.dtype, (T, n_head * v_head_dim), "gated output")
+        if gate_offset + n_head * v_head_dim > W:
+            _fail(f"a gate at column {gate_offset} does not fit rows of {W}")
+        self._call("retention", "gfb_retention_gate", _ptr(o), _ptr(src), c_int(_dt(src)), c_int(W), c_int(gate_offset), _ptr(out),
+                   c_int(T), c_int(n_head), c_int(v_head_dim), c_float(eps), _stream())
+
+    def activation(self, x, kind, out=None):
+        if kind not in _UNARY:
+            _fail(f"unknown activation '{kind}'")
+        out = x if out is None else out
+        _need(x, name="activation input")
+        _need(out, x.dtype, x.shape, "activation output")
+        self._call("elementwise", "gfb_activation", _ptr(x), _ptr(out), c_int(_dt(x)), c_long(x.numel()), c_int(_EPI[kind]), _stream())
+
     # -- matrix products -----------------------------------------------------------
     def linear(self, a, w, out, mode="store", defer=False):
         M, K = a.shape
@@ -200,6 +316,9 @@ class CudaKernels:
             _fail(f"product of {a.dtype} cannot be stored as {out.dtype}")
         self._label = f"linear {N}x{K} {mode}"
         if a.dtype == torch.bfloat16 and self._tc_fits(M, N, K, mode):
+            if mode in _UNARY:
+                self._linear_tc(a, w, out, "store")
+                return self.activation(out, mode)
             return self._linear_tc(a, w, out, mode, defer=defer and mode in ("store", "add"))
         if a.dtype == torch.float32 and out.dtype != torch.float32:
             _fail("a float32 product is stored as float32")
@@ -268,17 +387,21 @@ class CudaKernels:
         return None
 
     # -- attention ---------------------------------------------------------------------
-    def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None):
+    def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None):
         T = batch.n_tokens
+        dv = v_head_dim or head_dim
         _need(q, shape=(T, n_head, head_dim), name="q")
-        _need(out, q.dtype, (T, n_head * head_dim), "attention output")
+        _need(out, q.dtype, (T, n_head * dv), "attention output")
         _need(kv.k_pool, q.dtype, name="key pool")
-        if (q.dtype == torch.bfloat16 and kv.page_size == 64 and head_dim % 8 == 0 and head_dim <= 256
+        if sink is not None:
+            _need(sink, torch.float32, (n_head,), "sink")
+        plain = chunk is None and sink is None and dv == head_dim
+        if (plain and q.dtype == torch.bfloat16 and kv.page_size == 64 and head_dim % 8 == 0 and head_dim <= 256
                 and n_head // n_kv <= 8):
             return self._attention_bf16(q, kv, batch, out, n_head, n_kv, head_dim, scale, window)
         self._call("attention_generic", "gfb_attention_generic", _ptr(q), _ptr(out), c_int(_dt(q)),
-                   *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim),
-                   c_float(scale), c_int(window or 0), _ptr(batch.status), _stream())
+                   *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(dv),
+                   c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink), _ptr(batch.status), _stream())
 
     def decode_slices(self, max_kv_len, page_size, blocks) -> int:
         return decode_slices(max_kv_len, page_size, blocks, self.sm_count)

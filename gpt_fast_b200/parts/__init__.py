@@ -72,7 +72,7 @@ def build_block(layer, dim: int, dtype, position):
             raise KeyError(f"block '{layer.block}' asks for a part of kind '{kind}'; kinds: {sorted(REGISTRIES)}")
         extra = {"position": position} if kind == "mixer" else {}
         built[role] = build_part(REGISTRIES[kind], layer.parts[role], dtype=dtype, **extra)
-    return cls(parts=built, dim=dim, dtype=dtype)
+    return cls(parts=built, dim=dim, dtype=dtype, **dict(getattr(layer, "block_params", None) or {}))
 
 
 def build_part(table: Dict[str, Callable], spec: PartSpec, **extra: Any):
@@ -83,4 +83,4 @@ def build_part(table: Dict[str, Callable], spec: PartSpec, **extra: Any):
     return table[spec.kind](**spec.params, **extra)
 
 
-from . import norm, rope, attention, feed_forward, block  # noqa: E402,F401  (register the built-in parts)
+from . import norm, rope, attention, retention, feed_forward, block  # noqa: E402,F401  (register the built-in parts)

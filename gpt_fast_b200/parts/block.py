@@ -1,6 +1,7 @@
 """Arrangements of a layer's parts.  'prenorm' is gpt-fast's TransformerBlock
 (model.py:153-164): x += mixer(norm(x)); x += feed_forward(norm(x)), with the
-residual stream x kept in 32-bit.
+residual stream x kept in 32-bit.  'sandwich' norms a sublayer's output as well
+and scales it before the sum; its feed-forward is optional.
 
 An arrangement declares `roles`: the names of the parts it is made of, each with
 the kind of part that fills it ('mixer', 'feed_forward', 'norm': the registries of
@@ -9,7 +10,7 @@ and hands them over as a dict; mixers also receive the layer's position encoding
 import torch
 
 from . import register_block
-from .residual import as_residual
+from .residual import Branch, as_residual
 
 
 @register_block("prenorm")
@@ -37,3 +38,47 @@ class PreNormBlock:
         self.mixer.forward(h, batch, view, residual=x, append=append)
         self.ffn_norm.forward(x, h)
         self.feed_forward.forward(h, residual=x)
+
+
+@register_block("sandwich")
+class SandwichBlock:
+    """Norms on both sides of every sublayer and a constant factor on the branch:
+
+        x += mult * post_norm(mixer(pre_norm(x)));   x += mult * post_norm(feed_forward(pre_norm(x)))
+
+    The feed-forward (with its two norms) is optional: a layer without one has only the first sublayer.  A
+    sublayer writes into a `Branch` (32-bit); the normed sum is left to the stream, whose next norm does it on
+    the way (`Residual.add_normed`)."""
+    roles = {"mixer": "mixer", "mixer_norm": "norm", "mixer_post_norm": "norm",
+             "feed_forward": "feed_forward", "ffn_norm": "norm", "ffn_post_norm": "norm"}
+    optional_roles = ("feed_forward", "ffn_norm", "ffn_post_norm")
+
+    def __init__(self, parts: dict, dim: int, dtype: torch.dtype, residual_mult: float = 1.0):
+        self._parts = dict(parts)
+        ffn = [r for r in self.optional_roles if r in parts]
+        if ffn and len(ffn) != len(self.optional_roles):
+            raise ValueError(f"a sandwich block has a feed-forward with both of its norms or none of the three; got {ffn}")
+        self.mixer, self.mixer_norm, self.mixer_post_norm = parts["mixer"], parts["mixer_norm"], parts["mixer_post_norm"]
+        self.feed_forward = parts.get("feed_forward")
+        self.ffn_norm, self.ffn_post_norm = parts.get("ffn_norm"), parts.get("ffn_post_norm")
+        self.dim, self.dtype, self.mult = dim, dtype, float(residual_mult)
+
+    def parts(self):
+        return dict(self._parts)
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def forward(self, x, batch, view, append: bool = True):
+        x = as_residual(x)
+        T, dev = x.x.shape[0], x.x.device
+        h = torch.empty(T, self.dim, dtype=self.dtype, device=dev)
+        self.mixer_norm.forward(x, h)
+        y = Branch(T, self.dim, dev)
+        self.mixer.forward(h, batch, view, residual=y, append=append)
+        x.add_normed(y, self.mixer_post_norm, self.mult)
+        if self.feed_forward is not None:
+            self.ffn_norm.forward(x, h)
+            y = Branch(T, self.dim, dev)
+            self.feed_forward.forward(h, residual=y)
+            x.add_normed(y, self.ffn_post_norm, self.mult)

@@ -1,4 +1,4 @@
-"""SwiGLU feed-forward (gpt-fast model.py:219-227): w2(silu(w1 x) * w3 x).
+"""Feed-forwards.  SwiGLU (gpt-fast model.py:219-227): w2(silu(w1 x) * w3 x); `Dense`: down(act(up x)).
 
 w1 (gate) and w3 (up) are stored as one matrix whose rows alternate gate, up,
 so that one product yields both and its epilogue applies silu(gate) * up
@@ -34,3 +34,31 @@ class SwiGLU:
         act = torch.empty(h.shape[0], self.hidden, dtype=self.dtype, device=h.device)
         ops.linear(h, self.w13, act, mode="swiglu")
         as_residual(residual).add_linear(act, self.w2)
+
+
+@register_feed_forward("dense")
+class Dense:
+    """Two products with a unary activation between them: down(act(up x)).  activation: 'gelu' (the exact one,
+    0.5 z (1 + erf(z / sqrt 2))), 'gelu_tanh' or 'silu'; it is applied in the first product's epilogue."""
+
+    ACTIVATIONS = ("gelu", "gelu_tanh", "silu")
+
+    def __init__(self, dim: int, hidden: int, dtype: torch.dtype, activation: str = "gelu"):
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"unknown activation '{activation}'; known: {self.ACTIVATIONS}")
+        self.dim, self.hidden, self.dtype, self.activation = dim, hidden, dtype, activation
+        self.up = self.down = None
+
+    def param_specs(self):
+        return {"up": ParamSpec((self.hidden, self.dim)), "down": ParamSpec((self.dim, self.hidden))}
+
+    def load(self, tensors):
+        self.up, self.down = tensors["up"], tensors["down"]
+
+    def export(self):
+        return {"up": self.up, "down": self.down}
+
+    def forward(self, h, residual):
+        act = torch.empty(h.shape[0], self.hidden, dtype=self.dtype, device=h.device)
+        ops.linear(h, self.up, act, mode=self.activation)
+        as_residual(residual).add_linear(act, self.down)

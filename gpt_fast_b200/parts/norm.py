@@ -1,5 +1,5 @@
-"""RMSNorm (gpt-fast model.py:230-241): x * rsqrt(mean(x^2) + eps) * weight,
-with the statistics and the products in 32-bit."""
+"""Norms over the 32-bit residual stream.  RMSNorm (gpt-fast model.py:230-241): x * rsqrt(mean(x^2) + eps) * weight;
+LayerNorm: (x - mean) / sqrt(variance + eps) * weight + bias.  Statistics and products are 32-bit."""
 import torch
 
 from .. import ops
@@ -33,3 +33,48 @@ class RMSNorm:
         else:
             ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
+
+
+@register_norm("layernorm")
+class LayerNorm:
+    """Layer norm with weight and bias: (x - mean) / sqrt(variance + eps) * weight + bias, the variance being the
+    mean of the squared deviations, all in 32-bit.  Besides norming the stream it can add a normed branch to it
+    (`add_into`: x += mult * norm(y)), which a sandwich block uses behind each sublayer; when the stream still owes
+    such a sum as it is normed, one kernel does both."""
+
+    def __init__(self, dim: int, eps: float, dtype: torch.dtype):
+        self.dim, self.eps, self.dtype = dim, float(eps), dtype
+        self.weight = self.bias = None
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.dim,), "vector"), "bias": ParamSpec((self.dim,), "vector")}
+
+    def load(self, tensors):
+        self.weight, self.bias = tensors["weight"], tensors["bias"]
+        if self.bias.dtype != self.weight.dtype:
+            self.bias = self.bias.to(self.weight.dtype)
+
+    def export(self):
+        return {"weight": self.weight, "bias": self.bias}
+
+    def _branch_args(self, owed):
+        branch, norm, mult = owed
+        return (branch.value(), norm.weight, norm.bias, norm.eps, mult)
+
+    def forward(self, x, out, rows=None):
+        """x: the residual stream (a `Residual`, or a complete float32 tensor [T, dim]) -> out [R, dim] in the
+        compute dtype; `rows` (int32 [R]) picks input rows."""
+        if not isinstance(x, Residual):
+            ops.layernorm(x, self.weight, self.bias, self.eps, out, rows)
+            return out
+        owed = x.normed
+        if owed is not None and rows is None and isinstance(owed[1], LayerNorm) and x.pending is None:
+            x.take_normed()
+            ops.layernorm(x.x, self.weight, self.bias, self.eps, out, None, branch=self._branch_args(owed))
+        else:
+            ops.layernorm(x.tensor(), self.weight, self.bias, self.eps, out, rows)
+        return out
+
+    def add_into(self, x32, branch, mult: float) -> None:
+        """x32 (float32 [T, dim], complete) += mult * norm(branch)."""
+        ops.layernorm(x32, None, None, 0.0, None, None, branch=(branch.value(), self.weight, self.bias, self.eps, mult))

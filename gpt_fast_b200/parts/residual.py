@@ -1,15 +1,21 @@
 """The residual stream of a step: the float32 running sum x [T, dim] plus,
-possibly, partial sums that are still owed to it.
+possibly, something that is still owed to it.
 
 A product whose sum over K was split across blocks leaves its result as a few
 partial sums.  Instead of a kernel that only adds them up, the stream keeps
 them `pending` and the next kernel that reads x completes the sum on its way:
 RMSNorm does (it reads every element of x anyway), so split reduction, residual
-add and norm are one pass.  Parts use
+add and norm are one pass.  In the same way a block that norms a sublayer's
+output before it adds it (`add_normed`) leaves that sum to the next norm that
+reads x, which then does both norms in one pass over the row.  Parts use
 
-    residual.add_linear(a, w)    x += a @ w.T   (fused into the product's epilogue, or deferred)
-    residual.add(y)              x += y         (for parts that cannot fuse)
-    residual.tensor()            x, complete
+    residual.add_linear(a, w)        x += a @ w.T   (fused into the product's epilogue, or deferred)
+    residual.add(y)                  x += y         (for parts that cannot fuse)
+    residual.add_normed(y, norm, m)  x += m * norm(y), y a `Branch`  (deferred to the next norm, or resolved)
+    residual.tensor()                x, complete
+
+`Branch` is a stream of its own that starts empty: what a sublayer "adds" to it
+is its output, kept in 32-bit (or as the partial sums of its last product).
 """
 import torch
 
@@ -20,8 +26,12 @@ class Residual:
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.pending = None
+        self.normed = None                 # (Branch, norm part, factor) still to be added
 
     def resolve(self) -> None:
+        if self.normed is not None:
+            branch, norm, mult = self.take_normed()
+            norm.add_into(self.x, branch, mult)
         if self.pending is not None:
             ops.add_partials(self.x, self.pending)
             self.pending = None
@@ -38,9 +48,64 @@ class Residual:
         self.resolve()
         ops.add_into(self.x, y)
 
+    def add_normed(self, branch: "Branch", norm, mult: float) -> None:
+        self.resolve()
+        self.normed = (branch, norm, float(mult))
+
+    def take_normed(self):
+        n, self.normed = self.normed, None
+        return n
+
     def take_pending(self):
+        """The partial sums still owed to x (the caller adds them); a normed branch is added first."""
+        if self.normed is not None:
+            branch, norm, mult = self.take_normed()
+            norm.add_into(self.x, branch, mult)
         p, self.pending = self.pending, None
         return p
+
+
+class Branch(Residual):
+    """The output of one sublayer on its way into a stream: float32 [T, dim], empty at first, so the first
+    product "added" to it is stored, or left as the partial sums of a split over K (`partials`, x unwritten)."""
+
+    def __init__(self, n_tokens: int, dim: int, device):
+        super().__init__(torch.empty(n_tokens, dim, dtype=torch.float32, device=device))
+        self.empty = True
+        self.partials = None
+
+    def _materialise(self) -> None:
+        if self.empty:
+            self.x.zero_()
+            self.empty = False
+        if self.partials is not None:
+            p, self.partials = self.partials, None
+            self.x.zero_()
+            ops.add_partials(self.x, p)
+
+    def add_linear(self, a, w) -> None:
+        if self.empty:
+            self.partials = ops.linear(a, w, self.x, mode="store", defer=True)
+            self.empty = False
+            return
+        self._materialise()
+        super().add_linear(a, w)
+
+    def add(self, y) -> None:
+        self._materialise()
+        super().add(y)
+
+    def resolve(self) -> None:
+        self._materialise()
+        super().resolve()
+
+    def value(self) -> torch.Tensor:
+        """The branch as the norm kernels take it: the complete float32 [T, dim] tensor, or partial sums [S, T, dim]."""
+        if self.partials is not None and self.pending is None and self.normed is None:
+            p, self.partials = self.partials, None
+            self.empty = True
+            return p
+        return self.tensor()
 
 
 def as_residual(x) -> "Residual":

@@ -14,13 +14,18 @@ from .. import ops
 from . import register_position
 
 
-def rope_frequencies(head_dim: int, base: float, scaling: Optional[Dict[str, float]]) -> torch.Tensor:
-    """inv_freq[i] = base^(-2i/d) in 32-bit, i < d/2, then the llama3 rule:
+def rope_frequencies(head_dim: int, base: float, scaling: Optional[Dict[str, float]], freq_dtype: str = "float32") -> torch.Tensor:
+    """inv_freq[i] = base^(-2i/d) in 32-bit, i < d/2 (freq_dtype 'float64': evaluated in 64-bit and rounded once to
+    32-bit, which is the nearest 32-bit number to the exact power), then the llama3 rule:
     wavelengths shorter than original/high_freq_factor stay, longer than
     original/low_freq_factor are divided by `factor`, between them the two are
     blended linearly in original/wavelength."""
-    exponent = torch.arange(0, head_dim, 2, dtype=torch.float32)[: head_dim // 2] / head_dim
-    freqs = 1.0 / (base ** exponent)
+    if freq_dtype == "float64":
+        exponent = torch.arange(0, head_dim, 2, dtype=torch.float64)[: head_dim // 2] / head_dim
+        freqs = (float(base) ** -exponent).to(torch.float32)
+    else:
+        exponent = torch.arange(0, head_dim, 2, dtype=torch.float32)[: head_dim // 2] / head_dim
+        freqs = 1.0 / (base ** exponent)
     if scaling is None:
         return freqs
     factor, low, high = scaling["factor"], scaling["low_freq_factor"], scaling["high_freq_factor"]
@@ -42,16 +47,19 @@ def rope_frequencies(head_dim: int, base: float, scaling: Optional[Dict[str, flo
 
 @register_position("rope")
 class Rope:
-    """pairing 'interleaved': pairs (2i, 2i+1); 'half': pairs (i, i + d/2)."""
+    """pairing 'interleaved': pairs (2i, 2i+1); 'half': pairs (i, i + d/2).  `head_dim` is the number of rotated
+    dimensions; a mixer whose heads are larger leaves the rest as they are."""
 
     def __init__(self, head_dim: int, base: float, scaling: Optional[Dict[str, float]] = None,
-                 pairing: str = "interleaved"):
+                 pairing: str = "interleaved", freq_dtype: str = "float32"):
         if head_dim % 2:
             raise ValueError(f"rotary pairs need an even head_dim, got {head_dim}")
         if pairing not in ("interleaved", "half"):
             raise ValueError(f"unknown rotary pairing '{pairing}'")
+        if freq_dtype not in ("float32", "float64"):
+            raise ValueError(f"rotary frequencies are evaluated in float32 or float64, not '{freq_dtype}'")
         self.head_dim, self.base, self.scaling, self.pairing = head_dim, float(base), scaling, pairing
-        self.inv_freq = rope_frequencies(head_dim, self.base, scaling)
+        self.inv_freq = rope_frequencies(head_dim, self.base, scaling, freq_dtype)
         self.table = None
         self._retired = []                 # earlier, shorter tables: captured decode steps may still point at them
 

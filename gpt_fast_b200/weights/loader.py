@@ -102,7 +102,8 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 class RandomCheckpoint:
     """Seeded random tensors under the plan's checkpoint names: every matrix
-    N(0, std), every norm weight 1 + N(0, jitter).  Each tensor has a random
+    N(0, std), every norm weight 1 + N(0, jitter), every bias N(0, jitter), an embedding table and
+    other 'unit' vectors N(0, 1).  Each tensor has a random
     stream of its own, keyed by (seed, name), so the values do not depend on
     the order of reading.  Values are drawn in 32-bit on `gen_device` and
     rounded to the storage dtype."""
@@ -123,6 +124,12 @@ class RandomCheckpoint:
         x = torch.randn(s.shape, generator=g, device=self.gen_device, dtype=torch.float32)
         if s.init == "norm":
             x = (1.0 + x * self.jitter).to(self.vector_dtype)
+        elif s.init == "bias":
+            x = (x * self.jitter).to(self.vector_dtype)
+        elif s.init == "unit":
+            x = x.to(self.vector_dtype)
+        elif s.init == "embedding":
+            x = x.to(self.matrix_dtype)
         else:
             x = (x * self.std).to(self.matrix_dtype)
         return x.to(device)

@@ -76,6 +76,103 @@ class PlainOps:
         n = xr * torch.rsqrt((xr * xr).mean(-1, keepdim=True) + eps)
         out.copy_((n * weight.double()).to(out.dtype))
 
+    def layernorm(self, x, weight, bias, eps, out, rows=None, branch=None, rms=False):
+        def norm(v, w, b, e):
+            v = v.double()
+            if rms:
+                return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + e) * w.double()
+            dev = v - v.mean(-1, keepdim=True)
+            return dev * torch.rsqrt((dev * dev).mean(-1, keepdim=True) + e) * w.double() + b.double()
+        if branch is not None:
+            y, pw, pb, peps, mult = branch
+            if y.dim() == 3:
+                y = y.double().sum(0)
+            x.copy_((x.double() + mult * norm(y, pw, pb, peps)).float())
+        if out is not None:
+            xr = x if rows is None else x[rows.long()]
+            out.copy_(norm(xr, weight, bias, eps).to(out.dtype))
+
+    @staticmethod
+    def _rotate_front(v, cs, rot_dims, pairing):
+        """v [T, heads, d] (float64), cs [T, rot_dims/2, 2]: rotate the leading rot_dims dimensions."""
+        half = rot_dims // 2
+        c, s = cs[:, None, :, 0], cs[:, None, :, 1]
+        out = v.clone()
+        if pairing == "interleaved":
+            a, b = v[..., 0:rot_dims:2], v[..., 1:rot_dims:2]
+            out[..., 0:rot_dims:2], out[..., 1:rot_dims:2] = a * c - b * s, b * c + a * s
+        else:
+            a, b = v[..., :half], v[..., half:rot_dims]
+            out[..., :half], out[..., half:rot_dims] = a * c - b * s, b * c + a * s
+        return out
+
+    def qkv_prepare(self, src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table=None, rot_dims=0,
+                    pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True):
+        H, G, d, dv = n_head, n_kv, head_dim, v_head_dim
+        T = batch.n_tokens
+        x = (partials.double().sum(0) if partials is not None else src.double())
+        qo, ko, vo = offsets
+        q = x[:, qo:qo + H * d].reshape(T, H, d)
+        k = x[:, ko:ko + G * d].reshape(T, G, d)
+        v = x[:, vo:vo + G * dv].reshape(T, G, dv)
+        pos, slots = token_positions(batch)
+        if q_norm is not None:
+            q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + norm_eps) * q_norm.double()
+        if k_norm is not None:
+            k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + norm_eps) * k_norm.double()
+        if table is not None:
+            cs = table[pos].double()
+            q, k = self._rotate_front(q, cs, rot_dims, pairing), self._rotate_front(k, cs, rot_dims, pairing)
+        q_out.copy_(q.to(q_out.dtype))
+        if append:
+            page = kv.page_table.long()[slots, pos // kv.page_size]
+            if int(page.min()) < 0:
+                raise IndexError("token lands on a page the slot does not hold")
+            off = pos % kv.page_size
+            kv.k_pool[page, :, off] = (k * k_scale).to(kv.k_pool.dtype)
+            kv.v_pool[page, :, off] = v.to(kv.v_pool.dtype)
+
+    def retention(self, src, offsets, state, out, batch, n_head, head_dim, v_head_dim, decay, table=None, rot_dims=0,
+                  pairing="half", k_scale=1.0):
+        H, d, dv = n_head, head_dim, v_head_dim
+        T = batch.n_tokens
+        x = src.double()
+        qo, ko, vo = offsets
+        q = x[:, qo:qo + H * d].reshape(T, H, d)
+        k = x[:, ko:ko + H * d].reshape(T, H, d)
+        v = x[:, vo:vo + H * dv].reshape(T, H, dv)
+        pos, slots = token_positions(batch)
+        if table is not None:
+            cs = table[pos].double()
+            q, k = self._rotate_front(q, cs, rot_dims, pairing), self._rotate_front(k, cs, rot_dims, pairing)
+        k = k * k_scale
+        dec = decay.double()[:, None, None]
+        for t in range(T):                                    # packed tokens of one sequence are in order
+            slot = int(slots[t])
+            S = dec * state[slot].double() + k[t][:, :, None] * v[t][:, None, :]
+            state[slot] = S.float()
+            out[t] = torch.einsum("hdv,hd->hv", S, q[t]).float()
+
+    def retention_gate(self, o, src, gate_offset, out, n_head, v_head_dim, eps):
+        T = o.shape[0]
+        g = src[:, gate_offset:gate_offset + n_head * v_head_dim].double().reshape(T, n_head, v_head_dim)
+        od = o.double()
+        n = od * torch.rsqrt((od * od).mean(-1, keepdim=True) + eps)
+        out.copy_((n * (g / (1 + torch.exp(-g)))).reshape(T, -1).to(out.dtype))
+
+    @staticmethod
+    def _unary(z, kind):
+        if kind == "gelu":
+            return 0.5 * z * (1 + torch.erf(z / math.sqrt(2.0)))
+        if kind == "gelu_tanh":
+            return 0.5 * z * (1 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+        if kind == "silu":
+            return z / (1 + torch.exp(-z))
+        raise ValueError(kind)
+
+    def activation(self, x, kind, out=None):
+        (x if out is None else out).copy_(self._unary(x.double(), kind).to(x.dtype))
+
     def rope_table(self, inv_freq, table):
         ang = torch.arange(table.shape[0], dtype=torch.float32, device=table.device)[:, None] * inv_freq[None, :]
         table[..., 0] = torch.cos(ang.double()).float()
@@ -135,18 +232,23 @@ class PlainOps:
         elif mode == "swiglu":
             g, u = acc[:, 0::2], acc[:, 1::2]
             out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
+        elif mode in ("gelu", "gelu_tanh", "silu"):
+            out.copy_(self._unary(acc, mode).to(out.dtype))
         else:
             raise ValueError(mode)
 
     # -- attention -----------------------------------------------------------------------
-    def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None):
+    def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None):
         H, G, d = n_head, n_kv, head_dim
+        dv = v_head_dim or head_dim
         pos, slots = token_positions(batch)
         rep = H // G
-        res = torch.empty(batch.n_tokens, H, d, dtype=torch.float64, device=q.device)
+        res = torch.empty(batch.n_tokens, H, dv, dtype=torch.float64, device=q.device)
         for t in range(batch.n_tokens):
             p, slot = int(pos[t]), int(slots[t])
             lo = max(0, p - window + 1) if window else 0
+            if chunk:
+                lo = max(lo, p // chunk * chunk)
             j = torch.arange(lo, p + 1, device=q.device)
             pages = kv.page_table.long()[slot, j // kv.page_size]
             if int(pages.min()) < 0:
@@ -156,8 +258,12 @@ class PlainOps:
             k = k.repeat_interleave(rep, dim=1)
             v = v.repeat_interleave(rep, dim=1)
             s = torch.einsum("hd,nhd->hn", q[t].double(), k) * scale
-            res[t] = torch.einsum("hn,nhd->hd", torch.softmax(s, -1), v)
-        out.copy_(res.view(batch.n_tokens, H * d).to(out.dtype))
+            if sink is not None:
+                w = torch.softmax(torch.cat([s, sink.double()[:, None]], dim=-1), -1)[:, :-1]
+            else:
+                w = torch.softmax(s, -1)
+            res[t] = torch.einsum("hn,nhd->hd", w, v)
+        out.copy_(res.view(batch.n_tokens, H * dv).to(out.dtype))
 
     # -- sampling ----------------------------------------------------------------------------
     def argmax(self, logits, out):

@@ -331,6 +331,78 @@ def other_config(gf, torch, pk, name, steps, warmup):
     return res
 
 
+def llama_twin(cfg):
+    """A Llama config.json of the same width, depth, heads, vocabulary and (nearly) the same weight count per layer as a
+    Lasezen config: a SwiGLU of three matrices with 2/3 of the dense feed-forward's hidden size."""
+    W = cfg["width"]
+    ff = max(L["mlp"]["ff"] for L in cfg["layers"] if L["mlp"])
+    att = [L["mixer"] for L in cfg["layers"] if L["type"] == "attention"][0]
+    return {"model_type": "llama", "hidden_size": W, "num_attention_heads": W // att["dim"], "num_key_value_heads": att["kv_heads"],
+            "num_hidden_layers": len(cfg["layers"]), "intermediate_size": -(-(2 * ff // 3) // 256) * 256, "vocab_size": cfg["vocab"],
+            "max_position_embeddings": 16384, "rope_theta": 10000.0, "rms_norm_eps": 1e-5}
+
+
+def step_shares(gf, torch, ops, model, prompts, decode):
+    """ms per kind of kernel in ONE eager step (events around every launch, so nothing overlaps): a packed prefill of
+    `prompts`, or one decode step behind it."""
+    cache = model.new_cache(max_tokens=sum(pages_up(len(p) + 8) for p in prompts), max_seqs=len(prompts))
+    stepper = gf.Stepper(model, cache)
+    slots = cache.begin(len(prompts))
+    if decode:
+        stepper.step(slots, prompts, "last")
+        nxt = [[1]] * len(prompts)
+        stepper.step(slots, nxt, "last")
+    torch.cuda.synchronize()
+    with ops.trace() as rec:
+        stepper.step(slots, [[1]] * len(prompts) if decode else prompts, "last")
+    out = {}
+    for label, ms in ops.trace_times(rec):
+        kind = label.split(" ")[0] + (" " + label.split(" ")[-1] if label.startswith("linear") else "")
+        out[kind] = out.get(kind, 0.0) + ms
+    cache.end(slots)
+    return {k: round(v, 4) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
+
+
+def design_bench(a, design):
+    """Prefill and decode throughput of another design of the library at sizes that resemble a real model's layers (random
+    weights, bfloat16), beside the Llama decoder at equal size.  One JSON line; the default workload is untouched."""
+    import torch
+    import gpt_fast_b200 as gf
+    from gpt_fast_b200 import ops
+    from gpt_fast_b200.config.registry import config_from_name
+    if design != "lasezen":
+        print(f"bench.py: no size table for design '{design}'")
+        return 2
+    torch.cuda.set_device(0)
+    pk = peaks()
+    out = {"design": design, "dtype": "bf16", "data": "synthetic", "peaks": pk, "sizes": []}
+    with ClockSampler() as clocks:
+        for name, n_layers in (("lasezen-1b", None), ("lasezen-7b", a.layers or 8)):
+            cfg = config_from_name(name)
+            if n_layers:
+                cfg["layers"] = cfg["layers"][:n_layers]
+            row = {"size": name, "layers": len(cfg["layers"]), "width": cfg["width"]}
+            for label, source in ((design, cfg), ("llama", llama_twin(cfg))):
+                model = gf.load(source, dtype="bfloat16", device="cuda:0", random_weights=True, seed=0)
+                r = {"weight_gb": round(model.weight_bytes() / 1e9, 3)}
+                r["prefill_ms"] = {str(T): round(prefill_bench(gf, torch, model, T), 3) for T in (512, 2048, 8192)}
+                r["prefill_tok_s"] = {T: round(int(T) / ms * 1e3) for T, ms in r["prefill_ms"].items()}
+                r["decode_ms"], r["decode_tok_s"] = {}, {}
+                for batch in (1, 8, 64):
+                    prompts = random_prompts(torch, model.vocab_size, [512] * batch, 3)
+                    ms = decode_bench(gf, torch, model, prompts, 2048, a.steps, a.warmup)[0]
+                    r["decode_ms"][str(batch)], r["decode_tok_s"][str(batch)] = round(ms, 4), round(batch / ms * 1e3)
+                r["prefill_shares_ms"] = step_shares(gf, torch, ops, model, random_prompts(torch, model.vocab_size, [2048], 4), False)
+                r["decode_shares_ms"] = step_shares(gf, torch, ops, model, random_prompts(torch, model.vocab_size, [512] * 8, 5), True)
+                row[label] = r
+                del model
+                torch.cuda.empty_cache()
+            out["sizes"].append(row)
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm(a):
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
     try:
@@ -352,12 +424,16 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quicker)")
     ap.add_argument("--skip-configs", action="store_true", help="leave out the Llama-3.2-3B and Llama-2-13B sizes")
     ap.add_argument("--skip-shares", action="store_true", help="leave out the per-kernel shares")
+    ap.add_argument("--design", default=None, help="instead of the default workload: prefill and decode of another design "
+                    "(lasezen) at layer sizes of a real model, beside the Llama decoder at equal size")
     a = ap.parse_args()
     if a.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     if a.impl == "reference":
         return reference_arm(a)
+    if a.design:
+        return design_bench(a, a.design.lower())
 
     import torch
     import gpt_fast_b200 as gf

@@ -300,6 +300,9 @@ struct RopeSource {
     const int* lengths_early; // optional: the lengths to request the first pages on before the preceding kernel has
                               // ended (null: the batch's own); they are checked against the batch's own afterwards
     int one_each;             // every sequence brings exactly one token: token t is sequence t (two loads fewer)
+    // two options of the mask and the softmax that travel with this struct (both off when zero / null):
+    int chunk;                // a query sees only the keys of its own block of `chunk` positions (blocks from position 0)
+    const float* sink;        // [H], 32-bit: exp(sink_h) joins the denominator of head h and has no value
 };
 
 // x0[i], x1[i] = the elements e0[i], e1[i] of qkv for N pairs at once: from bfloat16, or as the sum of the S partial
@@ -404,6 +407,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     auto plan = [&](int len) {
         pos = len + q_off;
         lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        if (rs.chunk > 0) lo = max(lo, (pos / rs.chunk) * rs.chunk);
         first_page = lo / PAGE;
         last_page = pos / PAGE;
         const int n_pages = last_page - first_page + 1;
@@ -461,7 +465,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     };
     // A block that is its sequence's only slice and has no window starts at the table's first entry whatever the
     // length is: its entries are then asked for together with the length, not behind it.
-    const bool from_zero = splits == 1 && window <= 0;
+    const bool from_zero = splits == 1 && window <= 0 && rs.chunk <= 0;
     int ahead[DECODE_NBUF];                      // entries ahead_first .. ahead_first + DECODE_NBUF - 1
     int ahead_first = -1;
     auto entries_ahead = [&](int first) {
@@ -711,6 +715,14 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (mm != -INFINITY) l_all += lw[w * 8 + gq] * exp2f(mm - m_all);
     }
     float f = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_all);
+    if (splits == 1 && rs.sink != nullptr && gq < rep) {
+        // the sink's term joins the sum under the larger of the two maxima (with slices the combine kernel adds it)
+        const float sk = rs.sink[g * rep + gq] * 1.4426950408889634f;
+        const float m_fin = fmaxf(m_all, sk);
+        const float down = (m_all == -INFINITY) ? 0.f : exp2f(m_all - m_fin);
+        l_all = l_all * down + exp2f(sk - m_fin);
+        f *= down;
+    }
     if (splits == 1) f = l_all > 0.f ? f / l_all : 0.f;
 #pragma unroll
     for (int j = 0; j < NT; j++)
@@ -739,14 +751,16 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 }
 
 __global__ void attn_combine_kernel(const float* __restrict__ scratch_o, const float* __restrict__ scratch_ml,
-                                    __nv_bfloat16* __restrict__ out, int H, int d, int splits) {
+                                    __nv_bfloat16* __restrict__ out, int H, int d, int splits, const float* __restrict__ sink) {
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int t = blockIdx.x, head = blockIdx.y;
     const float* ml = scratch_ml + ((size_t)t * H + head) * splits * 2;
     float m = -INFINITY;
     for (int z = 0; z < splits; z++) m = fmaxf(m, ml[2 * z]);
-    float l = 0.f;
+    const float sk = sink != nullptr ? sink[head] * 1.4426950408889634f : -INFINITY;
+    m = fmaxf(m, sk);
+    float l = sink != nullptr ? exp2f(sk - m) : 0.f;
     for (int z = 0; z < splits; z++) l += (ml[2 * z] == -INFINITY) ? 0.f : ml[2 * z + 1] * exp2f(ml[2 * z] - m);
     float inv = l > 0.f ? 1.f / l : 0.f;
     for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
@@ -859,11 +873,28 @@ GFB_API long gfb_attn_decode_scratch_bytes(int T, int H, int d, int splits) {
     return splits > 1 ? (long)T * H * splits * (d + 2) * 4 : 0;
 }
 
+// The same with the two further options of mask and softmax: chunk > 0 (a query sees only keys of its own block of
+// `chunk` positions) and sink (float32 [H] or null: exp(sink_h) joins the denominator).  head_dim 64 or 128 only.
+GFB_API int gfb_attn_decode_masked(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                   int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                   const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                   int chunk, const float* sink, int splits, float* scratch, int* status, cudaStream_t stream);
+
 GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
                             int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
                             const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
                             int splits, float* scratch, int* status, cudaStream_t stream) {
+    return gfb_attn_decode_masked(q, out, k_pool, v_pool, page_table, max_pages, page_size, n_pages, cu_seqlens, tok_seq, slots,
+                                  lengths, n_seqs, n_tokens, H, G, d, scale, window, 0, nullptr, splits, scratch, status, stream);
+}
+
+GFB_API int gfb_attn_decode_masked(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                   int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                   const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                   int chunk, const float* sink, int splits, float* scratch, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if ((chunk > 0 || sink != nullptr) && d != 64 && d != 128)
+        return gfb_fail("gfb_attn_decode_masked: a block mask or a sink needs head_dim 64 or 128, got %d", d);
     if (page_size != PAGE) return gfb_fail("gfb_attn_decode: pages of %d tokens (the kernel is built for %d)", page_size, PAGE);
     if (d % 8 || d > THREADS * MAX_DPT) return gfb_fail("gfb_attn_decode: head_dim %d must be a multiple of 8, at most %d", d, THREADS * MAX_DPT);
     if (G <= 0 || H % G || H / G > MAX_REP) return gfb_fail("gfb_attn_decode: %d heads over %d groups (at most %d per group)", H, G, MAX_REP);
@@ -884,7 +915,10 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
     dim3 grid(n_tokens, G, splits);
     cudaError_t e;
     if (d == 128 || d == 64) {
-        e = launch_decode_mma(d, SRC_Q, grid, stream, q, out, so, sml, kv, b, H, G, scale, window, splits, status, RopeSource{}, 0);
+        RopeSource rs{};
+        rs.chunk = chunk;
+        rs.sink = sink;
+        e = launch_decode_mma(d, SRC_Q, grid, stream, q, out, so, sml, kv, b, H, G, scale, window, splits, status, rs, 0);
         if (e == cudaErrorInvalidValue && gfb_error_text[0]) return 1;
     } else {
         e = gfb_launch(attn_decode_kernel, grid, dim3(THREADS), smem, stream, (const __nv_bfloat16*)q,
@@ -894,7 +928,7 @@ GFB_API int gfb_attn_decode(const void* q, void* out, void* k_pool, void* v_pool
     if (splits > 1) {
         dim3 cgrid(n_tokens, H);
         e = gfb_launch(attn_combine_kernel, cgrid, dim3(128), 0, stream, (const float*)so, (const float*)sml,
-                       (__nv_bfloat16*)out, H, d, splits);
+                       (__nv_bfloat16*)out, H, d, splits, sink);
         return gfb_check(e, "gfb_attn_decode (combine)");
     }
     return 0;
@@ -927,7 +961,7 @@ GFB_API int gfb_attn_decode_rope(const void* src, int n_part, void* out, void* k
     float* so = scratch;
     float* sml = scratch ? scratch + (size_t)n_tokens * H * splits * d : nullptr;
     RopeSource rs{src, n_part, (size_t)n_tokens * (H + 2 * G) * d, table, table_len, pairing, append, lengths_early,
-                  n_tokens == n_seqs ? 1 : 0};
+                  n_tokens == n_seqs ? 1 : 0, 0, nullptr};
     const int pages = max_kv_len > 0 ? (max_kv_len + PAGE - 1) / PAGE : 0;
     cudaError_t e = launch_decode_mma(d, n_part > 0 ? SRC_PARTIALS : SRC_QKV, dim3(n_tokens, G, splits), stream, nullptr, out, so, sml,
                                       kv, b, H, G, scale, window, splits, status, rs, (pages + splits - 1) / splits);
@@ -935,7 +969,7 @@ GFB_API int gfb_attn_decode_rope(const void* src, int n_part, void* out, void* k
     if (gfb_check(e, "gfb_attn_decode_rope")) return 1;
     if (splits > 1) {
         e = gfb_launch(attn_combine_kernel, dim3(n_tokens, H), dim3(128), 0, stream, (const float*)so, (const float*)sml,
-                       (__nv_bfloat16*)out, H, d, splits);
+                       (__nv_bfloat16*)out, H, d, splits, (const float*)nullptr);
         return gfb_check(e, "gfb_attn_decode_rope (combine)");
     }
     return 0;

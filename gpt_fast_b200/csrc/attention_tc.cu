@@ -257,13 +257,21 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// The first key the query at `pos` sees: the window's edge, or the start of its block of `chunk` positions
+// (blocks counted from position 0), whichever is later.
+__device__ __forceinline__ int first_key(int pos, int window, int chunk) {
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
+    return lo;
+}
+
 // One (sequence, tile of TQ query tokens, key/value head) unit of work.
 struct TileWork {
     int seq, tq0, g;
-    int t_first, nq, slot, pos0, last_pos, first_lo, blk0, n_iter, last_page;
+    int t_first, nq, slot, pos0, last_pos, first_lo, last_lo, blk0, n_iter, last_page;
 };
 // Work item w of the grid's list (long tiles first: the tile index runs backwards); false: an empty item.
-__device__ __forceinline__ bool tile_work(const GfbBatch& b, int w, int n_x, int G, int TQ, int window, TileWork& t) {
+__device__ __forceinline__ bool tile_work(const GfbBatch& b, int w, int n_x, int G, int TQ, int window, int chunk, TileWork& t) {
     const int xi = w / G;
     t.g = w - xi * G;
     t.seq = -1;
@@ -281,7 +289,8 @@ __device__ __forceinline__ bool tile_work(const GfbBatch& b, int w, int n_x, int
     t.slot = b.slots[t.seq];
     t.pos0 = b.lengths[t.slot] + t.tq0;
     t.last_pos = t.pos0 + t.nq - 1;
-    t.first_lo = (window > 0 && t.pos0 - window + 1 > 0) ? t.pos0 - window + 1 : 0;
+    t.first_lo = first_key(t.pos0, window, chunk);
+    t.last_lo = first_key(t.last_pos, window, chunk);
     t.blk0 = t.first_lo / KEYS;
     t.n_iter = t.last_pos / KEYS + 1 - t.blk0;                   // key blocks [blk0, blk0 + n_iter)
     t.last_page = t.last_pos / PAGE;
@@ -305,7 +314,8 @@ __global__ void __launch_bounds__(320, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ page_table, int max_pages, int n_pages_pool,
-                       GfbBatch b, int H, int G, float scale_log2e, int window, int n_x, int* status) {
+                       GfbBatch b, int H, int G, float scale_log2e, int window, int chunk, const float* __restrict__ sink,
+                       int n_x, int* status) {
     extern __shared__ uint8_t smem_raw[];
     if (threadIdx.x == 0) { prefetch_map(&map_q); prefetch_map(&map_k); prefetch_map(&map_v); }
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -369,7 +379,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             bool ok = true;
             for (int pass = 0, w; (w = snake_item(pass, (int)blockIdx.x, (int)gridDim.x)) < n_work && ok; pass++) {
                 TileWork t;
-                if (!tile_work(b, w, n_x, G, TQ, window, t)) continue;
+                if (!tile_work(b, w, n_x, G, TQ, window, chunk, t)) continue;
                 const int* pt = page_table + (size_t)t.slot * max_pages;
                 if (it > 0) ok = mbar_wait(smem_u32(&bars->q_empty), (it - 1u) & 1u, abort_flag, status, 11);
                 if (!ok) break;
@@ -432,7 +442,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             };
             for (int pass = 0, w; (w = snake_item(pass, (int)blockIdx.x, (int)gridDim.x)) < n_work && ok; pass++) {
                 TileWork t;
-                if (!tile_work(b, w, n_x, G, TQ, window, t)) continue;
+                if (!tile_work(b, w, n_x, G, TQ, window, chunk, t)) continue;
                 ok = mbar_wait(smem_u32(&bars->q_full), it & 1u, abort_flag, status, 5);
                 ok = ok && issue_s(jj, t.n_iter == 1);
                 for (int j = 0; j < t.n_iter && ok; j++, jj++) {
@@ -469,10 +479,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         bool ok = true;
         for (int pass = 0, w; (w = snake_item(pass, (int)blockIdx.x, (int)gridDim.x)) < n_work && ok; pass++) {
             TileWork t;
-            if (!tile_work(b, w, n_x, G, TQ, window, t)) continue;
+            if (!tile_work(b, w, n_x, G, TQ, window, chunk, t)) continue;
             const bool row_ok = tq < t.nq;
             const int row_pos = t.pos0 + tq;
-            const int row_lo = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
+            const int row_lo = first_key(row_pos, window, chunk);
             float m_run = -INFINITY, l_run = 0.f;                        // l_run: this warp's half of the row's sum
             for (int j = 0; j < t.n_iter && ok; j++, jj++) {
                 const uint32_t sb = jj & 1u;
@@ -480,7 +490,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 ok = mbar_wait(smem_u32(&bars->s_full[sb]), (jj >> 1) & 1u, abort_flag, status, 8);
                 if (!ok) break;
                 tc_fence_after();
-                const bool need_mask = key0 + 63 > t.pos0 || key0 < t.first_lo || window > 0 || t.nq < TQ;
+                const bool need_mask = key0 + 63 > t.pos0 || key0 < t.last_lo || window > 0 || t.nq < TQ;
                 // this warp's half of the row into registers
                 uint32_t raw[2][32];
                 tmem_ld32_issue(lane_base + COL_S + sb * 128 + half * 64, raw[0]);
@@ -585,8 +595,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (!ok) break;
             l_run += bars->l_half[it & 1u][half ^ 1][r];
             it++;
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             const int head = t.g * rep + (r - tq * rep);
+            // a sink: one more term of the sum under the row's reference maximum, with no value behind it
+            if (sink != nullptr && m_run != -INFINITY) l_run += fast_exp2(sink[head] * 1.4426950408889634f - m_run * scale_log2e);
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = out + ((size_t)(t.t_first + t.tq0 + tq) * H + head) * DH + half * (DH / 2);   // each warp stores its half of the columns
 #pragma unroll 1
             for (int c = 0; c < NH; c++) {
@@ -642,7 +654,8 @@ __global__ void __launch_bounds__(320, 1)
 attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ page_table, int max_pages, int n_pages_pool,
-                        GfbBatch b, int H, int G, float scale_log2e, int window, int* status) {
+                        GfbBatch b, int H, int G, float scale_log2e, int window, int chunk, const float* __restrict__ sink,
+                        int* status) {
     extern __shared__ uint8_t smem_raw[];
     if (threadIdx.x == 0) { prefetch_map(&map_q); prefetch_map(&map_k); prefetch_map(&map_v); }
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -714,7 +727,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         nq[x] = min(TQ, qlen - (tq0 + x * TQ));
         pos0[x] = len0 + tq0 + x * TQ;
         if (nq[x] > 0) {
-            const int first_lo = (window > 0 && pos0[x] - window + 1 > 0) ? pos0[x] - window + 1 : 0;
+            const int first_lo = first_key(pos0[x], window, chunk);
             lo_blk[x] = first_lo / KEYS;
             hi_blk[x] = (pos0[x] + nq[x] - 1) / KEYS + 1;
         } else {
@@ -834,8 +847,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int tq = r / rep;
         const bool row_ok = tq < nq[x];
         const int row_pos = pos0[x] + tq;
-        const int row_lo = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
-        const int first_lo = (window > 0 && pos0[x] - window + 1 > 0) ? pos0[x] - window + 1 : 0;
+        const int row_lo = first_key(row_pos, window, chunk);
+        const int last_lo = first_key(pos0[x] + max(nq[x], 1) - 1, window, chunk);
         float m_run = -INFINITY, l_run = 0.f;
         uint32_t n_done = 0;                                             // blocks of this tile finished
         bool ok = true;
@@ -845,7 +858,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             ok = mbar_wait(smem_u32(&bars->s_full[x]), n_done & 1u, abort_flag, status, 8);
             if (!ok) break;
             tc_fence_after();
-            const bool need_mask = key0 + KEYS - 1 > pos0[x] || key0 < first_lo || window > 0 || nq[x] < TQ;
+            const bool need_mask = key0 + KEYS - 1 > pos0[x] || key0 < last_lo || window > 0 || nq[x] < TQ;
             float v[4][32];
             tmem_ld_row128(lane_base + col_s, v);
             if (need_mask) {
@@ -913,8 +926,9 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (ok && n_done > 0) ok = mbar_wait(smem_u32(&bars->pv_done[x]), (n_done - 1u) & 1u, abort_flag, status, 10);
         if (ok && n_done > 0) {
             tc_fence_after();
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             const int head = g * rep + (r - tq * rep);
+            if (sink != nullptr && m_run != -INFINITY) l_run += fast_exp2(sink[head] * 1.4426950408889634f - m_run * scale_log2e);
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = out + ((size_t)(t_first + tq0 + x * TQ + tq) * H + head) * D;
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
@@ -965,10 +979,25 @@ EncodeTiledFn encode_fn() {
 // Causal attention for runs of new tokens on tcgen05; head_dim 128, pages of 64, at most 8 heads per group
 // with 128 % (heads per group) == 0.  tiles: query tiles of 128 rows per block, 1 or 2, or 0 to let the
 // function choose by the amount of work.  max_blocks: cap of the one-tile kernel's grid (0: one block per SM).
+GFB_API int gfb_attn_prefill_tc_masked(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                       int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                       const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                       int chunk, const float* sink, int tiles, int max_blocks, int* status, cudaStream_t stream);
+
 GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
                                 int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
                                 const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
                                 int tiles, int max_blocks, int* status, cudaStream_t stream) {
+    return gfb_attn_prefill_tc_masked(q, out, k_pool, v_pool, page_table, max_pages, page_size, n_pages, cu_seqlens, tok_seq, slots,
+                                      lengths, n_seqs, n_tokens, H, G, d, scale, window, 0, nullptr, tiles, max_blocks, status, stream);
+}
+
+// The same with a block mask (chunk > 0: a query sees only the keys of its own block of `chunk` positions, blocks
+// counted from position 0) and a sink (float32 [H] or null: exp(sink_h) joins the softmax denominator of head h).
+GFB_API int gfb_attn_prefill_tc_masked(const void* q, void* out, void* k_pool, void* v_pool, const int* page_table, int max_pages,
+                                       int page_size, int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots,
+                                       const int* lengths, int n_seqs, int n_tokens, int H, int G, int d, float scale, int window,
+                                       int chunk, const float* sink, int tiles, int max_blocks, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (page_size != PAGE || (d != 64 && d != 128))
         return gfb_fail("gfb_attn_prefill_tc: built for pages of %d and head_dim 64 or 128, got %d and %d", PAGE, page_size, d);
@@ -1024,7 +1053,7 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
         }
         dim3 grid((n_tokens + 2 * TQ - 1) / (2 * TQ) + n_seqs, G);
         e = gfb_launch(attn_prefill_tc2_kernel, grid, dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                       page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, status);
+                       page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, status);
     } else {
         size_t smem = 1024 + (size_t)(1 + 2 * KV_STAGES) * TILE_BYTES + sizeof(Bars);
         static bool configured = false;
@@ -1040,10 +1069,10 @@ GFB_API int gfb_attn_prefill_tc(const void* q, void* out, void* k_pool, void* v_
         if (blocks > cap) blocks = cap;
         if (d == 128)
             e = gfb_launch(attn_prefill_tc_kernel<128>, dim3((unsigned)blocks), dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, n_x, status);
+                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, n_x, status);
         else
             e = gfb_launch(attn_prefill_tc_kernel<64>, dim3((unsigned)blocks), dim3(320), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
-                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, n_x, status);
+                           page_table, max_pages, n_pages, b, H, G, scale * 1.4426950408889634f, window, chunk, sink, n_x, status);
     }
     return gfb_check(e, "gfb_attn_prefill_tc");
 }

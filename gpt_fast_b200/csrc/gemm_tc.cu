@@ -27,7 +27,14 @@
 
 GFB_DEFINE_LAST_ERROR()
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_GELU = 4 };   // GELU: store gelu(acc), the exact (erf) form, as bfloat16
+
+// what a storing epilogue does to an accumulator value before it rounds it
+template <int EPI>
+__device__ __forceinline__ float fin(float x) {
+    if (EPI == EPI_GELU) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+    return x;
+}
 
 namespace {
 
@@ -298,8 +305,8 @@ __device__ __forceinline__ void epilogue_rows(float* stage, uint32_t taddr, int 
                 const float* a = stage + (size_t)(q * 32 + rr) * SP + c;
                 float4 lo = *reinterpret_cast<const float4*>(a), hi = *reinterpret_cast<const float4*>(a + 4);
                 uint4 pk;
-                pk.x = pack_bf16(lo.x, lo.y); pk.y = pack_bf16(lo.z, lo.w);
-                pk.z = pack_bf16(hi.x, hi.y); pk.w = pack_bf16(hi.z, hi.w);
+                pk.x = pack_bf16(fin<EPI>(lo.x), fin<EPI>(lo.y)); pk.y = pack_bf16(fin<EPI>(lo.z), fin<EPI>(lo.w));
+                pk.z = pack_bf16(fin<EPI>(hi.x), fin<EPI>(hi.y)); pk.w = pack_bf16(fin<EPI>(hi.z), fin<EPI>(hi.w));
                 *reinterpret_cast<uint4*>((__nv_bfloat16*)out + (size_t)(row0 + q * 32 + rr) * ldo + col0 + c) = pk;
             }
         }
@@ -460,8 +467,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                                 *reinterpret_cast<float4*>((float*)out + (size_t)m * ldo + rr) = v;
                             } else {
                                 uint2 pk;
-                                pk.x = pack_bf16(v.x, v.y);
-                                pk.y = pack_bf16(v.z, v.w);
+                                pk.x = pack_bf16(fin<EPI>(v.x), fin<EPI>(v.y));
+                                pk.y = pack_bf16(fin<EPI>(v.z), fin<EPI>(v.w));
                                 *reinterpret_cast<uint2*>((__nv_bfloat16*)out + (size_t)m * ldo + rr) = pk;
                             }
                         } else {
@@ -474,7 +481,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                                 } else if (EPI == EPI_PARTIAL) partial[((size_t)blockIdx.z * Cc + m) * R + r1] = e[u];
                                 else if (EPI == EPI_ADD) ((float*)out)[(size_t)m * ldo + r1] += e[u];
                                 else if (sizeof(TO) == 4) ((float*)out)[(size_t)m * ldo + r1] = e[u];
-                                else ((__nv_bfloat16*)out)[(size_t)m * ldo + r1] = __float2bfloat16_rn(e[u]);
+                                else ((__nv_bfloat16*)out)[(size_t)m * ldo + r1] = __float2bfloat16_rn(fin<EPI>(e[u]));
                             }
                         }
                     }
@@ -508,7 +515,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             if (EPI == EPI_PARTIAL) partial[((size_t)blockIdx.z * Cc + m) * R + r] = x;
                             else if (EPI == EPI_ADD) ((float*)out)[(size_t)m * ldo + r] += x;
                             else if (sizeof(TO) == 4) ((float*)out)[(size_t)m * ldo + r] = x;
-                            else ((__nv_bfloat16*)out)[(size_t)m * ldo + r] = __float2bfloat16_rn(x);
+                            else ((__nv_bfloat16*)out)[(size_t)m * ldo + r] = __float2bfloat16_rn(fin<EPI>(x));
                         }
                     }
                 }
@@ -629,8 +636,8 @@ __device__ __forceinline__ void drain_chunk(float* stage, uint32_t taddr, int c0
                 const float* a = stage + r * PSP + col;
                 float4 lo = *reinterpret_cast<const float4*>(a), hi = *reinterpret_cast<const float4*>(a + 4);
                 uint4 pk;
-                pk.x = pack_bf16(lo.x, lo.y); pk.y = pack_bf16(lo.z, lo.w);
-                pk.z = pack_bf16(hi.x, hi.y); pk.w = pack_bf16(hi.z, hi.w);
+                pk.x = pack_bf16(fin<EPI>(lo.x), fin<EPI>(lo.y)); pk.y = pack_bf16(fin<EPI>(lo.z), fin<EPI>(lo.w));
+                pk.z = pack_bf16(fin<EPI>(hi.x), fin<EPI>(hi.y)); pk.w = pack_bf16(fin<EPI>(hi.z), fin<EPI>(hi.w));
                 *reinterpret_cast<uint4*>((__nv_bfloat16*)out + (size_t)(grow0 + r) * ldo + gc + col) = pk;
             }
         }
@@ -1010,7 +1017,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TO* __re
         for (int s = 0; s < S; s++) acc += partial[((size_t)s * M + m) * N + n];
         if (EPI == EPI_ADD) ((float*)out)[(size_t)m * ldo + n] += acc;
         else if (sizeof(TO) == 4) ((float*)out)[(size_t)m * ldo + n] = acc;
-        else ((__nv_bfloat16*)out)[(size_t)m * ldo + n] = __float2bfloat16_rn(acc);
+        else ((__nv_bfloat16*)out)[(size_t)m * ldo + n] = __float2bfloat16_rn(fin<EPI>(acc));
     }
 }
 
@@ -1121,6 +1128,7 @@ int dispatch_epi(int epi, int out_dt, const CUtensorMap& mx, const CUtensorMap& 
     if (epi == EPI_PARTIAL) { if (SWAP) GO(EPI_PARTIAL, float); return gfb_fail("gfb_gemm_tc: a split over K needs the swapped orientation"); }
     if (epi == EPI_ADD) GO(EPI_ADD, float);
     if (epi == EPI_SWIGLU) GO(EPI_SWIGLU, bf16);
+    if (epi == EPI_GELU && out_dt == GFB_BF16) GO(EPI_GELU, bf16);
     if (epi == EPI_STORE && out_dt == GFB_F32) GO(EPI_STORE, float);
     if (epi == EPI_STORE && out_dt == GFB_BF16) GO(EPI_STORE, bf16);
 #undef GO
@@ -1142,6 +1150,7 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
     if (K <= 0 || K % 8) return gfb_fail("gfb_gemm_tc: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
     if (N % 8) return gfb_fail("gfb_gemm_tc: N = %d must be a multiple of 8", N);
     if (epi == EPI_SWIGLU && N % 16) return gfb_fail("gfb_gemm_tc: SwiGLU needs N %% 16 == 0, got %d", N);
+    if (epi == EPI_GELU && out_dt != GFB_BF16) return gfb_fail("gfb_gemm_tc: the GELU epilogue stores bfloat16");
     if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)out) & 15) return gfb_fail("gfb_gemm_tc: operands must be 16-byte aligned");
     if (stages < 2 || stages > MAX_STAGES) return gfb_fail("gfb_gemm_tc: stages = %d out of range", stages);
     if (bn < 512 && smem_bytes(bn, stages) > 227 * 1024) return gfb_fail("gfb_gemm_tc: %d stages of a %d-column tile exceed shared memory", stages, bn);
@@ -1178,6 +1187,7 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
         typedef __nv_bfloat16 bf16;
         if (epi == EPI_ADD) return launch_pair<EPI_ADD, float>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
         if (epi == EPI_SWIGLU) return launch_pair<EPI_SWIGLU, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
+        if (epi == EPI_GELU) return launch_pair<EPI_GELU, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
         if (out_dt == GFB_F32) return launch_pair<EPI_STORE, float>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
         return launch_pair<EPI_STORE, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
     }
@@ -1196,6 +1206,7 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
         typedef __nv_bfloat16 bf16;
         if (epi == EPI_ADD) return launch_persistent<EPI_ADD, float>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
         if (epi == EPI_SWIGLU) return launch_persistent<EPI_SWIGLU, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
+        if (epi == EPI_GELU) return launch_persistent<EPI_GELU, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
         if (out_dt == GFB_F32) return launch_persistent<EPI_STORE, float>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
         return launch_persistent<EPI_STORE, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
     }
@@ -1217,6 +1228,7 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
 #define RED(E, T) e = gfb_launch(splitk_reduce_kernel<E, T>, grid, dim3(256), 0, stream, (const float*)workspace, (T*)out, splits, M, N, ldo)
         if (epi == EPI_ADD) RED(EPI_ADD, float);
         else if (epi == EPI_SWIGLU) RED(EPI_SWIGLU, bf16);
+        else if (epi == EPI_GELU) RED(EPI_GELU, bf16);
         else if (out_dt == GFB_F32) RED(EPI_STORE, float);
         else RED(EPI_STORE, bf16);
 #undef RED

@@ -316,7 +316,8 @@ class CudaKernels:
             _fail(f"product of {a.dtype} cannot be stored as {out.dtype}")
         self._label = f"linear {N}x{K} {mode}"
         if a.dtype == torch.bfloat16 and self._tc_fits(M, N, K, mode):
-            if mode in _UNARY:
+            if mode in _UNARY and not (mode == "gelu" and out.dtype == torch.bfloat16):
+                # only the exact GELU has an epilogue of its own in the tensor-core kernel
                 self._linear_tc(a, w, out, "store")
                 return self.activation(out, mode)
             return self._linear_tc(a, w, out, mode, defer=defer and mode in ("store", "add"))
@@ -395,10 +396,11 @@ class CudaKernels:
         _need(kv.k_pool, q.dtype, name="key pool")
         if sink is not None:
             _need(sink, torch.float32, (n_head,), "sink")
-        plain = chunk is None and sink is None and dv == head_dim
-        if (plain and q.dtype == torch.bfloat16 and kv.page_size == 64 and head_dim % 8 == 0 and head_dim <= 256
-                and n_head // n_kv <= 8):
-            return self._attention_bf16(q, kv, batch, out, n_head, n_kv, head_dim, scale, window)
+        plain = chunk is None and sink is None
+        if (dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
+                and (head_dim in (64, 128) or (plain and head_dim % 8 == 0 and head_dim <= 256))):
+            # the tensor-core kernels; a block mask or a sink only at the head sizes they are built for
+            return self._attention_bf16(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk=chunk, sink=sink)
         self._call("attention_generic", "gfb_attention_generic", _ptr(q), _ptr(out), c_int(_dt(q)),
                    *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(dv),
                    c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink), _ptr(batch.status), _stream())
@@ -407,25 +409,27 @@ class CudaKernels:
         return decode_slices(max_kv_len, page_size, blocks, self.sm_count)
 
     def _attention_bf16(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window, splits=None, prefill=None, tiles=0,
-                        max_blocks=0):
+                        max_blocks=0, chunk=None, sink=None):
         T = batch.n_tokens
         if prefill is None:
             prefill = splits is None and batch.max_q_len > 1 and head_dim in (64, 128)
         if prefill and head_dim in (64, 128) and n_head // n_kv <= 8:
-            self._call("attention_tc", "gfb_attn_prefill_tc", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
-                       c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(tiles),
-                       c_int(max_blocks), _ptr(batch.status), _stream())
+            self._call("attention_tc", "gfb_attn_prefill_tc_masked", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
+                       c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink),
+                       c_int(tiles), c_int(max_blocks), _ptr(batch.status), _stream())
             return
         if splits is None:
             splits = 1
             if batch.max_q_len == 1:
-                splits = self.decode_slices(batch.max_kv_len, kv.page_size, T * n_kv)
+                # a query reads at most its own block of `chunk` positions (and the page that block starts in)
+                reach = batch.max_kv_len if not chunk else min(batch.max_kv_len, chunk + kv.page_size)
+                splits = self.decode_slices(reach, kv.page_size, T * n_kv)
         scratch = None
         if splits > 1:
             scratch = torch.empty(T * n_head * splits * (head_dim + 2), dtype=torch.float32, device=q.device)
-        self._call("attention_bf16", "gfb_attn_decode", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
-                   c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(splits),
-                   _ptr(scratch), _ptr(batch.status), _stream())
+        self._call("attention_bf16", "gfb_attn_decode_masked", _ptr(q), _ptr(out), *self._kv_args(kv), *self._batch_args(batch),
+                   c_int(n_head), c_int(n_kv), c_int(head_dim), c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink),
+                   c_int(splits), _ptr(scratch), _ptr(batch.status), _stream())
 
     def rope_append_attention(self, qkv, partials, kv, batch, table, out, n_head, n_kv, head_dim, pairing, append,
                               scale, window=None, lengths_early=None) -> bool:

@@ -62,7 +62,8 @@ def test_layernorm_uses_deviations_not_raw_squares():
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("kind", ["gelu", "gelu_tanh", "silu"])
-@pytest.mark.parametrize("M,N,K", [(5, 72, 40), (1, 256, 128), (150, 384, 256), (700, 512, 256), (33, 100, 50)])
+@pytest.mark.parametrize("M,N,K", [(5, 72, 40), (1, 256, 128), (150, 384, 256), (700, 512, 256), (33, 100, 50), (8, 256, 2048),
+                                   (64, 512, 1024), (130, 1024, 512)])
 def test_linear_with_activation(dtype, kind, M, N, K):
     a, w = rnd(M, K, dtype=dtype, seed=1), rnd(N, K, dtype=dtype, scale=0.2, seed=2)
     out = torch.empty(M, N, dtype=dtype, device=DEV)
@@ -137,7 +138,7 @@ def test_qkv_prepare(dtype, H, G, d, dv, rot, pairing, norm):
 
 # ---- attention with a block mask, a sink and its own value head size ------------------------------------------------------
 
-def run_attention(dtype, q_lens, starts, H, G, d, dv, chunk, sink, scale, k_all, v_all, q_all):
+def run_attention(dtype, q_lens, starts, H, G, d, dv, chunk, sink, scale, k_all, v_all, q_all, force=None):
     """Put every sequence's keys and values (positions 0 .. start + q_len - 1) into pages and attend with the last
     q_len queries.  k_all / v_all / q_all: per sequence [len, G, d], [len, G, dv], [len, H, d] (float)."""
     batch, table, n_pages = make_batch(q_lens, starts, len(q_lens) + 2, 64, max(-(-(s + q) // 64) for s, q in zip(starts, q_lens)), seed=4)
@@ -153,7 +154,10 @@ def run_attention(dtype, q_lens, starts, H, G, d, dv, chunk, sink, scale, k_all,
         qs.append(q_all[s][p0:p0 + n])
     q = torch.cat(qs).to(dtype).to(DEV).contiguous()
     out = torch.empty(batch.n_tokens, H * dv, dtype=dtype, device=DEV)
-    ops.attention(q, PagedKV(kp, vp, table, 64), batch, out, H, G, d, scale, None, chunk, sink, dv)
+    if force is None:
+        ops.attention(q, PagedKV(kp, vp, table, 64), batch, out, H, G, d, scale, None, chunk, sink, dv)
+    else:                                                    # one of the tensor-core kernels, named
+        ops.kernels()._attention_bf16(q, PagedKV(kp, vp, table, 64), batch, out, H, G, d, scale, None, chunk=chunk, sink=sink, **force)
     ops.check_status(batch.status)
     return out
 
@@ -173,6 +177,66 @@ def test_attention_block_mask_and_sink(dtype, H, G, d, dv, chunk):
         want = pl.sink_softmax_attention(q_all[s], k_all[s], v_all[s], d64(sink), 0.3, chunk)[p0:].reshape(n, H * dv)
         torch.testing.assert_close(d64(out[at:at + n]), want, **tol(dtype))
         at += n
+
+
+@pytest.mark.parametrize("force", [dict(prefill=True, tiles=1), dict(prefill=True, tiles=2), dict(splits=1), dict(splits=3)],
+                         ids=["prefill-one-tile", "prefill-two-tiles", "decode", "decode-three-slices"])
+@pytest.mark.parametrize("H,G,d,chunk", [(8, 1, 64, 64), (4, 4, 128, 48), (6, 2, 128, 200), (8, 2, 64, 5), (2, 1, 128, 4096), (5, 1, 64, None)])
+def test_tensor_core_attention_with_block_mask_and_sink(force, H, G, d, chunk):
+    """The bfloat16 tensor-core kernels (prefill on tcgen05, one or two query tiles; decode, one slice or several)
+    with the block mask and the sink, where blocks end inside pages, inside query tiles and between sequences."""
+    if force.get("tiles") == 2 and d != 128:
+        pytest.skip("the two-tile kernel is built for heads of 128")
+    dtype = torch.bfloat16
+    decode = "splits" in force
+    q_lens, starts = ([1, 1, 1, 1, 1], [0, 63, 64, 300, 511]) if decode else ([300, 1, 70, 3, 129], [0, 63, 130, 126, 383])
+    g = torch.Generator().manual_seed(9)
+    L = [s + n for s, n in zip(starts, q_lens)]
+    R = lambda *shape: torch.randn(*shape, generator=g).to(dtype).double()
+    k_all, v_all, q_all = [R(n, G, d) for n in L], [R(n, G, d) for n in L], [R(n, H, d) for n in L]
+    sink = torch.randn(H, generator=g).to(DEV) * 2
+    out = run_attention(dtype, q_lens, starts, H, G, d, d, chunk, sink, 0.2, k_all, v_all, q_all, force)
+    at = 0
+    for s, (n, p0) in enumerate(zip(q_lens, starts)):
+        want = pl.sink_softmax_attention(q_all[s], k_all[s], v_all[s], d64(sink), 0.2, chunk)[p0:].reshape(n, H * d)
+        torch.testing.assert_close(d64(out[at:at + n]), want, rtol=3e-2, atol=3e-2)
+        at += n
+    if chunk and chunk < 300:                               # the mask matters at these sizes: plain causal attention differs
+        causal = pl.sink_softmax_attention(q_all[-1], k_all[-1], v_all[-1], d64(sink), 0.2, None)[starts[-1]:].reshape(q_lens[-1], H * d)
+        assert (causal - d64(out[at - q_lens[-1]:at])).abs().max() > 0.1
+
+
+@pytest.mark.parametrize("force", [None, dict(prefill=True, tiles=1), dict(prefill=True, tiles=2), dict(splits=1), dict(splits=2)],
+                         ids=["dispatch", "prefill-one-tile", "prefill-two-tiles", "decode", "decode-two-slices"])
+def test_tensor_core_attention_block_edges_and_sink_share(force):
+    """As the test below, for the tensor-core kernels: the key at the first position of the query's block is found,
+    the one before it is not seen; and a sink equal to the only visible score takes half of the weight."""
+    dtype, H, G, d, chunk = torch.bfloat16, 2, 1, 128, 48
+    p = 48 * 6 + 40
+    decode = force is not None and "splits" in force
+    g = torch.Generator().manual_seed(10)
+    for key_at, seen in ((288, True), (287, False), (p, True), (3, False)):
+        k = torch.randn(p + 1, G, d, generator=g) * 0.1
+        v = torch.randn(p + 1, G, d, generator=g)
+        q = torch.randn(p + 1, H, d, generator=g) * 0.1
+        q[p, :, 0] = 40.0
+        k[key_at, :, 0] = 40.0
+        sink = torch.full((H,), -30.0, device=DEV)
+        q_lens, starts = ([1], [p]) if decode else ([p + 1], [0])
+        out = run_attention(dtype, q_lens, starts, H, G, d, d, chunk, sink, 1.0, [k], [v], [q], force)[-1].float().cpu().view(H, d)
+        target = v[key_at, 0].to(dtype).float()
+        if seen:
+            torch.testing.assert_close(out, target.expand(H, d), rtol=2e-2, atol=2e-2)
+        else:
+            assert (out - target).abs().max() > 0.3, f"the key at {key_at} lies outside the block of {p} and was seen"
+    # position 96 starts a block: its own key is all it sees
+    k, v, q = torch.zeros(97, G, d), torch.ones(97, G, d) * 2.0, torch.zeros(97, H, d)
+    k[:, 0, 0], q[:, :, 0] = 2.0, 3.0                       # every score is 6 * scale = 1.5
+    q_lens, starts = ([1], [96]) if decode else ([97], [0])
+    for sink_value, share in ((1.5, 0.5), (60.0, 0.0), (-60.0, 1.0)):
+        sink = torch.full((H,), sink_value, device=DEV)
+        out = run_attention(dtype, q_lens, starts, H, G, d, d, chunk, sink, 0.25, [k], [v], [q], force)[-1:].float().cpu()
+        torch.testing.assert_close(out, torch.full((1, H * d), 2.0 * share), rtol=1e-2, atol=1e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

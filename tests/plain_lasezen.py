@@ -135,8 +135,9 @@ def retention_mixer(h, P, pre, mx, eps, act=None):
     return rounded(o, act) @ P[pre + "o"].to(f).T
 
 
-def dense_ff(h, P, pre, act=None):
-    return rounded(gelu_erf(rounded(h @ P[pre + "up"].to(h.dtype).T, act)), act) @ P[pre + "down"].to(h.dtype).T
+def dense_ff(h, P, pre, act=None, round_before_gelu=True):
+    z = h @ P[pre + "up"].to(h.dtype).T
+    return rounded(gelu_erf(rounded(z, act) if round_before_gelu else z), act) @ P[pre + "down"].to(h.dtype).T
 
 
 def layer_runs(cfg):
@@ -147,8 +148,10 @@ def layer_runs(cfg):
     return list(range(loop["start"])) + span * loop["times"] + list(range(loop["stop"], n))
 
 
-def forward(tokens, P, cfg, dtype=torch.float64, act=None, keep_layers=False):
-    """Logits [S, vocab] of one whole sequence (and, with keep_layers, the residual stream after every layer run)."""
+def forward(tokens, P, cfg, dtype=torch.float64, act=None, keep_layers=False, round_before_gelu=True):
+    """Logits [S, vocab] of one whole sequence (and, with keep_layers, the residual stream after every layer run).
+    round_before_gelu (only with act): whether the feed-forward's first product is rounded before the activation
+    (a kernel that applies the activation to its 32-bit accumulator does not)."""
     eps = float(cfg["norm"]["eps"])
     m = float(cfg["residual_mult"])
     f = dtype
@@ -165,7 +168,7 @@ def forward(tokens, P, cfg, dtype=torch.float64, act=None, keep_layers=False):
         x = x + m * ln(mixer(h, P, pre + "mix.", L["mixer"], eps, act), pre + "norm1b")
         if L.get("mlp") is not None:
             h = rounded(ln(x, pre + "norm2"), act)
-            x = x + m * ln(dense_ff(h, P, pre + "mlp.", act), pre + "norm2b")
+            x = x + m * ln(dense_ff(h, P, pre + "mlp.", act, round_before_gelu), pre + "norm2b")
         kept.append(x)
     logits = rounded(ln(x, "final.norm"), act) @ P["head"].to(f).T
     return (logits, torch.stack(kept)) if keep_layers else logits

@@ -74,6 +74,115 @@ __global__ void layernorm_kernel(float* __restrict__ x, const float* __restrict_
     }
 }
 
+// The same with the row in registers: float4 loads and stores, every load of a row (the branch, its partial sums, x)
+// in flight at once, and the statistics from the registers.  For D % 4 == 0 and D <= 4 * LN_VEC * blockDim.
+constexpr int LN_VEC = 8;
+
+__device__ __forceinline__ float4 ld_w4(const void* p, int dt, int i4) {
+    if (dt == GFB_BF16) {
+        const uint2 raw = reinterpret_cast<const uint2*>(p)[i4];
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    return reinterpret_cast<const float4*>(p)[i4];
+}
+
+// (mean, 1 / sqrt(mean of squared deviations + eps)) of the row spread over the block's registers
+__device__ __forceinline__ float2 reg_stats(const float4 (&v)[LN_VEC], int nvec, int D, float eps, int rms, float* scratch) {
+    float mean = 0.f;
+    if (!rms) {
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < LN_VEC; k++)
+            if ((int)threadIdx.x + k * (int)blockDim.x < nvec) s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        mean = gfb_block_sum(s, scratch) / (float)D;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < LN_VEC; k++)
+        if ((int)threadIdx.x + k * (int)blockDim.x < nvec) {
+            const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
+            ss += (a * a + b * b) + (c * c + d * d);
+        }
+    ss = gfb_block_sum(ss, scratch);
+    return make_float2(mean, 1.0f / sqrtf(ss / (float)D + eps));
+}
+
+template <typename TO>
+__global__ void layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, int S, size_t slice,
+                                     const void* pw, const void* pb, int p_dt, float peps, float mult,
+                                     const void* w, const void* b, int w_dt, float eps, TO* __restrict__ out,
+                                     const int* __restrict__ rows, int D, int rms) {
+    __shared__ float scratch[32];
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int r = blockIdx.x;
+    const int nvec = D >> 2;
+    const size_t base = (size_t)(rows ? rows[r] : r) * D;
+    float4 v[LN_VEC];
+    float4* xr = reinterpret_cast<float4*>(x + base);
+#pragma unroll
+    for (int k = 0; k < LN_VEC; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        v[k] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (y != nullptr) {
+        float4 u[LN_VEC];
+#pragma unroll
+        for (int k = 0; k < LN_VEC; k++) {
+            const int i = threadIdx.x + k * blockDim.x;
+            u[k] = i < nvec ? reinterpret_cast<const float4*>(y + base)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int p = 1; p < S; p++) {                       // further partial sums, ascending, a row's loads together
+            const float4* pr = reinterpret_cast<const float4*>(y + (size_t)p * slice + base);
+            float4 a[LN_VEC];
+#pragma unroll
+            for (int k = 0; k < LN_VEC; k++) {
+                const int i = threadIdx.x + k * blockDim.x;
+                a[k] = i < nvec ? pr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int k = 0; k < LN_VEC; k++) { u[k].x += a[k].x; u[k].y += a[k].y; u[k].z += a[k].z; u[k].w += a[k].w; }
+        }
+        const float2 st = reg_stats(u, nvec, D, peps, rms, scratch);
+#pragma unroll
+        for (int k = 0; k < LN_VEC; k++) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < nvec) {
+                const float4 g = ld_w4(pw, p_dt, i);
+                float4 n = make_float4((u[k].x - st.x) * st.y * g.x, (u[k].y - st.x) * st.y * g.y,
+                                       (u[k].z - st.x) * st.y * g.z, (u[k].w - st.x) * st.y * g.w);
+                if (!rms) { const float4 c = ld_w4(pb, p_dt, i); n.x += c.x; n.y += c.y; n.z += c.z; n.w += c.w; }
+                v[k].x += mult * n.x; v[k].y += mult * n.y; v[k].z += mult * n.z; v[k].w += mult * n.w;
+                xr[i] = v[k];
+            }
+        }
+    }
+    if (out == nullptr) return;
+    const float2 st = reg_stats(v, nvec, D, eps, rms, scratch);
+#pragma unroll
+    for (int k = 0; k < LN_VEC; k++) {
+        const int i = threadIdx.x + k * blockDim.x;
+        if (i < nvec) {
+            const float4 g = ld_w4(w, w_dt, i);
+            float4 n = make_float4((v[k].x - st.x) * st.y * g.x, (v[k].y - st.x) * st.y * g.y,
+                                   (v[k].z - st.x) * st.y * g.z, (v[k].w - st.x) * st.y * g.w);
+            if (!rms) { const float4 c = ld_w4(b, w_dt, i); n.x += c.x; n.y += c.y; n.z += c.z; n.w += c.w; }
+            TO* o = out + (size_t)r * D + 4 * i;
+            if (sizeof(TO) == 4) {
+                *reinterpret_cast<float4*>(o) = n;
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(n.x, n.y), hi = __floats2bfloat162_rn(n.z, n.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(o) = pk;
+            }
+        }
+    }
+}
+
 // x float32 [T, D].  y (or null): float32 [max(S,1)][T][D] (S = 0 or 1: one tensor; S > 1: partial sums), with its norm
 // (pw, pb, p_dt, peps) and the factor mult.  out (or null): [R, D] of type out_dt with its norm (w, b, w_dt, eps);
 // rows (or null) gathers input rows for `out` and cannot be combined with y.
@@ -84,9 +193,27 @@ GFB_API int gfb_layernorm(float* x, const float* y, int S, long slice, const voi
     if (y != nullptr && rows != nullptr) return gfb_fail("gfb_layernorm: a branch sum cannot be combined with a row gather");
     if (y == nullptr && out == nullptr) return 0;
     if ((size_t)D * sizeof(float) > 200 * 1024) return gfb_fail("gfb_layernorm: a row of %d elements does not fit shared memory", D);
+    cudaError_t e;
+    const bool aligned = (((uintptr_t)x | (uintptr_t)y | (uintptr_t)out | (uintptr_t)w | (uintptr_t)b | (uintptr_t)pw | (uintptr_t)pb) & 15) == 0;
+    if (D % 4 == 0 && slice % 4 == 0 && aligned && D <= 4 * LN_VEC * 1024) {
+        // few rows: many threads with one or two vectors each (the row's latency is what counts); many rows: fewer
+        // threads with up to eight, so that more rows are resident per SM
+        const int per = R <= 256 ? 2 : LN_VEC;
+        int vthreads = ((D / 4 + per - 1) / per + 31) / 32 * 32;
+        if (vthreads < 64) vthreads = 64;
+        if (vthreads > 1024) vthreads = 1024;
+        if (D / 4 <= LN_VEC * vthreads) {
+#define VGO(TO) e = gfb_launch(layernorm_vec_kernel<TO>, dim3(R), dim3(vthreads), 0, stream, x, y, S, (size_t)slice, pw, pb, p_dt, peps, \
+                               mult, w, b, w_dt, eps, (TO*)out, rows, D, rms)
+            if (out == nullptr || out_dt == GFB_F32) VGO(float);
+            else if (out_dt == GFB_BF16) VGO(__nv_bfloat16);
+            else return gfb_fail("gfb_layernorm: unknown output type %d", out_dt);
+#undef VGO
+            return gfb_check(e, "gfb_layernorm (vector)");
+        }
+    }
     const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
     const size_t smem = (size_t)D * sizeof(float);
-    cudaError_t e;
 #define GO(TO)                                                                                                         \
     do {                                                                                                               \
         static size_t allowed = 48 * 1024;                                                                             \

@@ -206,6 +206,283 @@ retention_kernel(const T* __restrict__ src, int width, int q_off, int k_off, int
     }
 }
 
+// ---- long prompts: the chunks of a sequence side by side ---------------------------------------------------------
+// The loop above walks through a sequence's chunks one after the other, so a single long prompt keeps only
+// (heads x value slices) blocks busy.  For prompts of more than one chunk the same sums are cut into three launches
+// whose blocks are independent:
+//   1. per chunk:    U_c = sum_j decay^(n-1-j) k_j v_j^T                                  (chunk_state_kernel)
+//   2. per element:  S before chunk c, by the scan S <- decay^n S + U_c over the sequence's chunks; U_c is
+//                    overwritten by the state BEFORE chunk c and the last S goes to the cache  (chunk_scan_kernel)
+//   3. per chunk:    o_i = sum_j A[i][j] v_j + decay^(i+1) S_c^T q_i                         (chunk_out_kernel)
+// Chunks are numbered through the batch (sequence after sequence); `w` below is that number.  Thread (ty, tx) of the
+// 16 x 16 grid owns rows 4 ty .. 4 ty + 3 and columns 4 tx .. 4 tx + 3 of a product, and both operands of every
+// product lie in shared memory so that its four values are one 16-byte load.
+constexpr int PC = 64;           // tokens per chunk
+constexpr int CP = PC + 4;       // row length of the transposed tiles ([dimension][token])
+
+struct ChunkWork { int seq, slot, t0, n, pos0, first; };   // first: whether it is its sequence's first chunk
+
+__device__ __forceinline__ bool chunk_work(const GfbBatch& b, int w, ChunkWork& c) {
+    int left = w;
+    for (int i = 0; i < b.n_seqs; i++) {
+        const int q0 = b.cu_seqlens[i], qlen = b.cu_seqlens[i + 1] - q0;
+        const int nc = (qlen + PC - 1) / PC;
+        if (left < nc) {
+            c.seq = i;
+            c.slot = b.slots[i];
+            c.t0 = q0 + left * PC;
+            c.n = min(PC, qlen - left * PC);
+            c.pos0 = b.lengths[c.slot] + left * PC;
+            c.first = left == 0;
+            return true;
+        }
+        left -= nc;
+    }
+    return false;
+}
+
+// (cos, sin) of pair u at position pos, or (1, 0) beyond the table (reported)
+__device__ __forceinline__ float2 rot_of(const float* table, int table_len, int half, int pos, int u, int* status, int token) {
+    if (pos >= 0 && pos < table_len) return make_float2(table[((size_t)pos * half + u) * 2], table[((size_t)pos * half + u) * 2 + 1]);
+    if (u == 0) gfb_report(status, GFB_ERR_CACHE_RANGE, token, pos);
+    return make_float2(1.f, 0.f);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+chunk_state_kernel(const T* __restrict__ src, int width, int k_off, int v_off, float* __restrict__ U, GfbBatch b,
+                   const float* __restrict__ table, int table_len, int rot_dims, int pairing, const float* __restrict__ decay,
+                   float k_scale, int H, int dk, int dv, int* status) {
+    extern __shared__ __align__(16) float smem[];
+    const int dk4 = (dk + 3) & ~3;
+    float* Kc = smem;                               // [PC][dk4]: rotated k times its factor and decay^(n-1-j)
+    float* Vs = Kc + (size_t)PC * dk4;              // [PC][VS]
+    float* pw = Vs + (size_t)PC * VS;               // [PC+1]
+    gfb_pdl_launch();
+    const int w = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * VS;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const float dec = decay[h];
+    for (int n = tid; n <= PC; n += THREADS) pw[n] = (float)pow((double)dec, (double)n);
+    gfb_pdl_wait();
+    ChunkWork c;
+    if (!chunk_work(b, w, c)) return;
+    __syncthreads();
+    const int half = rot_dims >> 1, per_tok = dk4 - half;
+    for (int e = tid; e < PC * per_tok; e += THREADS) {
+        const int j = e / per_tok, u = e - j * per_tok;
+        float* kd = Kc + (size_t)j * dk4;
+        if (j >= c.n) {                              // rows beyond the chunk add nothing
+            if (u < half) { kd[pairing == 1 ? u : 2 * u] = 0.f; kd[pairing == 1 ? u + half : 2 * u + 1] = 0.f; }
+            else kd[rot_dims + (u - half)] = 0.f;
+            continue;
+        }
+        const T* kh = src + (size_t)(c.t0 + j) * width + k_off + h * dk;
+        const float f = k_scale * pw[c.n - 1 - j];
+        if (u < half) {
+            const float2 cs = rot_of(table, table_len, half, c.pos0 + j, u, status, c.t0 + j);
+            const int i0 = pairing == 1 ? u : 2 * u, i1 = pairing == 1 ? u + half : 2 * u + 1;
+            const float ka = gfb_to_f32(kh[i0]), kb = gfb_to_f32(kh[i1]);
+            kd[i0] = (ka * cs.x - kb * cs.y) * f;
+            kd[i1] = (kb * cs.x + ka * cs.y) * f;
+        } else {
+            const int i0 = rot_dims + (u - half);
+            kd[i0] = i0 < dk ? gfb_to_f32(kh[i0]) * f : 0.f;
+        }
+    }
+    for (int e = tid; e < PC * VS; e += THREADS) {
+        const int j = e / VS, v = e - j * VS;
+        Vs[e] = (j < c.n && v0 + v < dv) ? gfb_to_f32(src[(size_t)(c.t0 + j) * width + v_off + h * dv + v0 + v]) : 0.f;
+    }
+    __syncthreads();
+    float* Ug = U + ((size_t)w * H + h) * dk * dv;
+    for (int d0 = 0; d0 < dk; d0 += 64) {
+        if (d0 + 4 * ty >= dk4) continue;
+        float acc[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) acc[r][cc] = 0.f;
+        for (int j = 0; j < c.n; j++) {
+            const float4 k4 = *reinterpret_cast<const float4*>(Kc + (size_t)j * dk4 + d0 + 4 * ty);
+            const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * VS + 4 * tx);
+            const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) acc[r][cc] = fmaf(kk[r], vv[cc], acc[r][cc]);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int d = d0 + 4 * ty + r;
+            if (d >= dk) continue;
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) {
+                const int v = v0 + 4 * tx + cc;
+                if (v < dv) Ug[(size_t)d * dv + v] = acc[r][cc];
+            }
+        }
+    }
+}
+
+// One thread per element of a (sequence, head)'s state: U[c] <- S before chunk c, S <- decay^n S + U[c]; the last S is stored.
+__global__ void __launch_bounds__(256)
+chunk_scan_kernel(float* __restrict__ U, float* __restrict__ state, GfbBatch b, const float* __restrict__ decay, int H, int dk, int dv) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int s = blockIdx.y, h = blockIdx.z;
+    const size_t per = (size_t)dk * dv;
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per) return;
+    int first = 0;                                   // number of the sequence's first chunk
+    for (int i = 0; i < s; i++) first += (b.cu_seqlens[i + 1] - b.cu_seqlens[i] + PC - 1) / PC;
+    const int qlen = b.cu_seqlens[s + 1] - b.cu_seqlens[s];
+    const int nc = (qlen + PC - 1) / PC;
+    if (nc == 0) return;
+    const float dec = decay[h];
+    const float full = (float)pow((double)dec, (double)PC);
+    const float last = (float)pow((double)dec, (double)(qlen - (nc - 1) * PC));
+    float* Sg = state + ((size_t)b.slots[s] * H + h) * per + e;
+    float S = *Sg;
+    for (int c = 0; c < nc; c++) {
+        float* u = U + ((size_t)(first + c) * H + h) * per + e;
+        const float add = *u;
+        *u = S;
+        S = (c == nc - 1 ? last : full) * S + add;
+    }
+    *Sg = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+chunk_out_kernel(const T* __restrict__ src, int width, int q_off, int k_off, int v_off, const float* __restrict__ U,
+                 float* __restrict__ out, GfbBatch b, const float* __restrict__ table, int table_len, int rot_dims, int pairing,
+                 const float* __restrict__ decay, float k_scale, int H, int dk, int dv, int* status) {
+    extern __shared__ __align__(16) float smem[];
+    float* Qt = smem;                               // [dk][CP]: rotated q, token fastest
+    float* Kt = Qt + (size_t)dk * CP;               // [dk][CP]: rotated k times its factor
+    float* Vs = Kt + (size_t)dk * CP;               // [PC][VS]
+    float* At = Vs + (size_t)PC * VS;               // [PC][CP]: At[j][i] = (q_i . k_j) decay^(i-j) for j <= i
+    float* Ss = At + (size_t)PC * CP;               // [dk][VS]: the state before this chunk
+    float* pw = Ss + (size_t)dk * VS;               // [PC+1]
+    gfb_pdl_launch();
+    const int w = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * VS;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const float dec = decay[h];
+    for (int n = tid; n <= PC; n += THREADS) pw[n] = (float)pow((double)dec, (double)n);
+    gfb_pdl_wait();
+    ChunkWork c;
+    if (!chunk_work(b, w, c)) return;
+    const int half = rot_dims >> 1, per_tok = dk - half;
+    for (int e = tid; e < PC * per_tok; e += THREADS) {
+        const int i = e / per_tok, u = e - i * per_tok;
+        const bool live = i < c.n;
+        const T* row = src + (size_t)(c.t0 + (live ? i : 0)) * width;
+        const T* qh = row + q_off + h * dk;
+        const T* kh = row + k_off + h * dk;
+        if (u < half) {
+            const int i0 = pairing == 1 ? u : 2 * u, i1 = pairing == 1 ? u + half : 2 * u + 1;
+            float q0 = 0.f, q1 = 0.f, k0 = 0.f, k1 = 0.f;
+            if (live) {
+                const float2 cs = rot_of(table, table_len, half, c.pos0 + i, u, nullptr, 0);
+                const float qa = gfb_to_f32(qh[i0]), qb = gfb_to_f32(qh[i1]), ka = gfb_to_f32(kh[i0]), kb = gfb_to_f32(kh[i1]);
+                q0 = qa * cs.x - qb * cs.y; q1 = qb * cs.x + qa * cs.y;
+                k0 = (ka * cs.x - kb * cs.y) * k_scale; k1 = (kb * cs.x + ka * cs.y) * k_scale;
+            }
+            Qt[(size_t)i0 * CP + i] = q0; Qt[(size_t)i1 * CP + i] = q1;
+            Kt[(size_t)i0 * CP + i] = k0; Kt[(size_t)i1 * CP + i] = k1;
+        } else {
+            const int i0 = rot_dims + (u - half);
+            Qt[(size_t)i0 * CP + i] = live ? gfb_to_f32(qh[i0]) : 0.f;
+            Kt[(size_t)i0 * CP + i] = live ? gfb_to_f32(kh[i0]) * k_scale : 0.f;
+        }
+    }
+    for (int e = tid; e < PC * VS; e += THREADS) {
+        const int j = e / VS, v = e - j * VS;
+        Vs[e] = (j < c.n && v0 + v < dv) ? gfb_to_f32(src[(size_t)(c.t0 + j) * width + v_off + h * dv + v0 + v]) : 0.f;
+    }
+    const float* Ug = U + ((size_t)w * H + h) * dk * dv;
+    for (int e = tid; e < dk * VS; e += THREADS) {
+        const int d = e / VS, v = e - d * VS;
+        Ss[e] = (v0 + v < dv) ? Ug[(size_t)d * dv + v0 + v] : 0.f;
+    }
+    __syncthreads();
+    {   // A, rows i = 4 ty + r, columns j = 4 tx + cc; stored transposed
+        float acc[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) acc[r][cc] = 0.f;
+        if (4 * tx <= 4 * ty + 3) {                    // tiles above the diagonal stay zero
+            for (int d = 0; d < dk; d++) {
+                const float4 q4 = *reinterpret_cast<const float4*>(Qt + (size_t)d * CP + 4 * ty);
+                const float4 k4 = *reinterpret_cast<const float4*>(Kt + (size_t)d * CP + 4 * tx);
+                const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int cc = 0; cc < 4; cc++) acc[r][cc] = fmaf(qq[r], kk[cc], acc[r][cc]);
+            }
+        }
+#pragma unroll
+        for (int cc = 0; cc < 4; cc++) {
+            const int j = 4 * tx + cc;
+            float a[4];
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const int i = 4 * ty + r;
+                a[r] = (j <= i && i < c.n) ? acc[r][cc] * pw[i - j] : 0.f;
+            }
+            *reinterpret_cast<float4*>(At + (size_t)j * CP + 4 * ty) = make_float4(a[0], a[1], a[2], a[3]);
+        }
+    }
+    __syncthreads();
+    if (4 * ty < c.n) {
+        float acc[4][4], carry[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) { acc[r][cc] = 0.f; carry[r][cc] = 0.f; }
+        const int jmax = min(c.n, 4 * ty + 4);           // A[i][j] = 0 beyond the row's own position
+        for (int j = 0; j < jmax; j++) {
+            const float4 a4 = *reinterpret_cast<const float4*>(At + (size_t)j * CP + 4 * ty);
+            const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * VS + 4 * tx);
+            const float aa[4] = {a4.x, a4.y, a4.z, a4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) acc[r][cc] = fmaf(aa[r], vv[cc], acc[r][cc]);
+        }
+        for (int d = 0; d < dk; d++) {
+            const float4 q4 = *reinterpret_cast<const float4*>(Qt + (size_t)d * CP + 4 * ty);
+            const float4 s4 = *reinterpret_cast<const float4*>(Ss + d * VS + 4 * tx);
+            const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) carry[r][cc] = fmaf(qq[r], ss[cc], carry[r][cc]);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int i = 4 * ty + r;
+            if (i >= c.n) continue;
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) {
+                const int v = v0 + 4 * tx + cc;
+                if (v < dv) out[((size_t)(c.t0 + i) * H + h) * dv + v] = acc[r][cc] + pw[i + 1] * carry[r][cc];
+            }
+        }
+    }
+}
+
+static size_t chunk_state_smem(int dk) { return ((size_t)PC * ((dk + 3) & ~3) + (size_t)PC * VS + PC + 1) * sizeof(float); }
+static size_t chunk_out_smem(int dk) { return ((size_t)2 * dk * CP + (size_t)PC * VS + (size_t)PC * CP + (size_t)dk * VS + PC + 1) * sizeof(float); }
+
+// Floats of scratch the three-launch form needs for a step of n_tokens tokens in n_seqs sequences (0: it does not apply).
+GFB_API long gfb_retention_scratch_floats(int n_tokens, int n_seqs, int max_q_len, int H, int dk, int dv) {
+    if (max_q_len <= PC || chunk_out_smem(dk) > 220 * 1024) return 0;
+    return ((long)(n_tokens + PC - 1) / PC + n_seqs) * H * dk * dv;
+}
+
 static size_t retention_smem(int C, int dk) {
     return ((size_t)2 * C * (dk + 1) + (size_t)C * VS + (size_t)C * (C + 1) + (size_t)dk * VS + C + 1) * sizeof(float);
 }
@@ -216,12 +493,44 @@ static size_t retention_smem(int C, int dk) {
 GFB_API int gfb_retention(const void* src, int dt, int width, int q_off, int k_off, int v_off, float* state, float* out,
                           const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths, int n_seqs,
                           int n_tokens, int max_q_len, const float* table, int table_len, int rot_dims, int pairing,
-                          const float* decay, float k_scale, int H, int dk, int dv, int* status, cudaStream_t stream) {
+                          const float* decay, float k_scale, int H, int dk, int dv, float* scratch, long scratch_floats,
+                          int* status, cudaStream_t stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
     if (table == nullptr) rot_dims = 0;
     if (rot_dims % 2 || rot_dims > dk || rot_dims < 0) return gfb_fail("gfb_retention: %d rotated dimensions in a head of %d", rot_dims, dk);
     if (H > 65535) return gfb_fail("gfb_retention: %d heads exceed the grid", H);
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
+    const long need = gfb_retention_scratch_floats(n_tokens, n_seqs, max_q_len, H, dk, dv);
+    if (need > 0 && scratch != nullptr && scratch_floats >= need) {
+        // prompts of several chunks: the chunks side by side, in three launches
+        const int n_chunks = (n_tokens + PC - 1) / PC + n_seqs;       // an upper bound; surplus blocks find no work
+        if (n_chunks > 0x7fffffff / 2 || n_seqs > 65535) return gfb_fail("gfb_retention: too many chunks or sequences");
+        dim3 cgrid(n_chunks, H, (dv + VS - 1) / VS);
+        const size_t s1 = chunk_state_smem(dk), s3 = chunk_out_smem(dk);
+        cudaError_t e;
+#define GO3(T)                                                                                                         \
+        do {                                                                                                           \
+            static bool configured = false;                                                                            \
+            if (!configured) {                                                                                         \
+                cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);  \
+                cudaFuncSetAttribute(chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);    \
+                configured = true;                                                                                     \
+            }                                                                                                          \
+            e = gfb_launch(chunk_state_kernel<T>, cgrid, dim3(THREADS), s1, stream, (const T*)src, width, k_off, v_off, scratch, b, \
+                           table, table_len, rot_dims, pairing, decay, k_scale, H, dk, dv, status);                    \
+            if (e == cudaSuccess)                                                                                      \
+                e = gfb_launch(chunk_scan_kernel, dim3((unsigned)(((size_t)dk * dv + 255) / 256), n_seqs, H), dim3(256), 0, stream, \
+                               scratch, state, b, decay, H, dk, dv);                                                   \
+            if (e == cudaSuccess)                                                                                      \
+                e = gfb_launch(chunk_out_kernel<T>, cgrid, dim3(THREADS), s3, stream, (const T*)src, width, q_off, k_off, v_off, \
+                               (const float*)scratch, out, b, table, table_len, rot_dims, pairing, decay, k_scale, H, dk, dv, status); \
+        } while (0)
+        if (dt == GFB_BF16) GO3(__nv_bfloat16);
+        else if (dt == GFB_F32) GO3(float);
+        else return gfb_fail("gfb_retention: unknown type %d", dt);
+#undef GO3
+        return gfb_check(e, "gfb_retention (chunks side by side)");
+    }
     dim3 grid(n_seqs, H, (dv + VS - 1) / VS);
     // 64 tokens at a time where that fits beside the state slice; 16 for decode steps and very large heads
     const size_t limit = 220 * 1024;

@@ -278,11 +278,17 @@ class CudaKernels:
             _need(table, torch.float32, name="rotary table")
             if table.shape[1] * 2 != rot_dims:
                 _fail(f"the rotary table serves {table.shape[1] * 2} dimensions, the mixer rotates {rot_dims}")
+        # prompts of several chunks run their chunks side by side and need room for one state per chunk
+        fn = self._f("retention", "gfb_retention_scratch_floats")
+        fn.restype = c_long
+        need = fn(c_int(T), c_int(batch.n_seqs), c_int(int(batch.max_q_len)), c_int(n_head), c_int(head_dim), c_int(v_head_dim))
+        fn.restype = c_long
+        scratch = torch.empty(need, dtype=torch.float32, device=src.device) if need > 0 else None
         self._call("retention", "gfb_retention", _ptr(src), c_int(_dt(src)), c_int(W), c_int(q_off), c_int(k_off), c_int(v_off),
                    _ptr(state), _ptr(out), *self._batch_args(batch), c_int(int(batch.max_q_len)), _ptr(table),
                    c_int(table.shape[0] if table is not None else 0), c_int(rot_dims if table is not None else 0),
                    c_int(_PAIRING[pairing]), _ptr(decay), c_float(k_scale), c_int(n_head), c_int(head_dim), c_int(v_head_dim),
-                   _ptr(batch.status), _stream())
+                   _ptr(scratch), c_long(need), _ptr(batch.status), _stream())
 
     def retention_gate(self, o, src, gate_offset, out, n_head, v_head_dim, eps):
         T, W = src.shape

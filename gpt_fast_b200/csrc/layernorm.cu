@@ -110,7 +110,8 @@ __device__ __forceinline__ float2 reg_stats(const float4 (&v)[LN_VEC], int nvec,
 }
 
 template <typename TO>
-__global__ void layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, int S, size_t slice,
+__global__ void __launch_bounds__(256)
+layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, int S, size_t slice,
                                      const void* pw, const void* pb, int p_dt, float peps, float mult,
                                      const void* w, const void* b, int w_dt, float eps, TO* __restrict__ out,
                                      const int* __restrict__ rows, int D, int rms) {
@@ -195,13 +196,14 @@ GFB_API int gfb_layernorm(float* x, const float* y, int S, long slice, const voi
     if ((size_t)D * sizeof(float) > 200 * 1024) return gfb_fail("gfb_layernorm: a row of %d elements does not fit shared memory", D);
     cudaError_t e;
     const bool aligned = (((uintptr_t)x | (uintptr_t)y | (uintptr_t)out | (uintptr_t)w | (uintptr_t)b | (uintptr_t)pw | (uintptr_t)pb) & 15) == 0;
-    if (D % 4 == 0 && slice % 4 == 0 && aligned && D <= 4 * LN_VEC * 1024) {
-        // few rows: many threads with one or two vectors each (the row's latency is what counts); many rows: fewer
-        // threads with up to eight, so that more rows are resident per SM
-        const int per = R <= 256 ? 2 : LN_VEC;
+    if (D % 4 == 0 && slice % 4 == 0 && aligned && D <= 4 * LN_VEC * 256) {
+        // few rows: many threads (up to 256) with few vectors each (the row's latency is what counts); many rows:
+        // fewer threads with up to eight, so that more rows are resident per SM
+        int per = R <= 256 ? 2 : LN_VEC;
+        if ((D / 4 + per - 1) / per > 256) per = (D / 4 + 255) / 256;
         int vthreads = ((D / 4 + per - 1) / per + 31) / 32 * 32;
         if (vthreads < 64) vthreads = 64;
-        if (vthreads > 1024) vthreads = 1024;
+        if (vthreads > 256) vthreads = 256;
         if (D / 4 <= LN_VEC * vthreads) {
 #define VGO(TO) e = gfb_launch(layernorm_vec_kernel<TO>, dim3(R), dim3(vthreads), 0, stream, x, y, S, (size_t)slice, pw, pb, p_dt, peps, \
                                mult, w, b, w_dt, eps, (TO*)out, rows, D, rms)

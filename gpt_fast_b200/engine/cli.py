@@ -36,7 +36,7 @@ def _prompt_arg(x):
 
 
 def build_parser():
-    p = argparse.ArgumentParser(description="Generate tokens with a Llama 2/3 model on one B200.")
+    p = argparse.ArgumentParser(description="Generate tokens with a model of this library (Llama 2/3, Lasezen) on one B200.")
     p.add_argument("--prompt", type=_prompt_arg, default="Hello, my name is",
                    help="Input prompt. An integer (or comma list of integers) generates synthetic prompts of those lengths.")
     p.add_argument("--num_samples", type=int, default=5, help="Number of samples.")

@@ -89,18 +89,19 @@ __device__ __forceinline__ float4 ld_w4(const void* p, int dt, int i4) {
 }
 
 // (mean, 1 / sqrt(mean of squared deviations + eps)) of the row spread over the block's registers
-__device__ __forceinline__ float2 reg_stats(const float4 (&v)[LN_VEC], int nvec, int D, float eps, int rms, float* scratch) {
+template <int NV>
+__device__ __forceinline__ float2 reg_stats(const float4 (&v)[NV], int nvec, int D, float eps, int rms, float* scratch) {
     float mean = 0.f;
     if (!rms) {
         float s = 0.f;
 #pragma unroll
-        for (int k = 0; k < LN_VEC; k++)
+        for (int k = 0; k < NV; k++)
             if ((int)threadIdx.x + k * (int)blockDim.x < nvec) s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
         mean = gfb_block_sum(s, scratch) / (float)D;
     }
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < LN_VEC; k++)
+    for (int k = 0; k < NV; k++)
         if ((int)threadIdx.x + k * (int)blockDim.x < nvec) {
             const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
             ss += (a * a + b * b) + (c * c + d * d);
@@ -109,7 +110,9 @@ __device__ __forceinline__ float2 reg_stats(const float4 (&v)[LN_VEC], int nvec,
     return make_float2(mean, 1.0f / sqrtf(ss / (float)D + eps));
 }
 
-template <typename TO>
+// NV: float4 per thread; W: partial sums of the branch whose loads are in flight together (a decode step's few rows
+// wait for one trip to L2 instead of one per partial sum; the sums are added in ascending order all the same).
+template <typename TO, int NV, int W>
 __global__ void __launch_bounds__(256)
 layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, int S, size_t slice,
                                      const void* pw, const void* pb, int p_dt, float peps, float mult,
@@ -121,34 +124,41 @@ layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, int S, 
     const int r = blockIdx.x;
     const int nvec = D >> 2;
     const size_t base = (size_t)(rows ? rows[r] : r) * D;
-    float4 v[LN_VEC];
+    float4 v[NV];
     float4* xr = reinterpret_cast<float4*>(x + base);
 #pragma unroll
-    for (int k = 0; k < LN_VEC; k++) {
+    for (int k = 0; k < NV; k++) {
         const int i = threadIdx.x + k * blockDim.x;
         v[k] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (y != nullptr) {
-        float4 u[LN_VEC];
+        float4 u[NV];
 #pragma unroll
-        for (int k = 0; k < LN_VEC; k++) {
+        for (int k = 0; k < NV; k++) {
             const int i = threadIdx.x + k * blockDim.x;
             u[k] = i < nvec ? reinterpret_cast<const float4*>(y + base)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        for (int p = 1; p < S; p++) {                       // further partial sums, ascending, a row's loads together
-            const float4* pr = reinterpret_cast<const float4*>(y + (size_t)p * slice + base);
-            float4 a[LN_VEC];
+        for (int p = 1; p < S; p += W) {                    // further partial sums, ascending, W of them loaded together
+            float4 a[W][NV];
 #pragma unroll
-            for (int k = 0; k < LN_VEC; k++) {
-                const int i = threadIdx.x + k * blockDim.x;
-                a[k] = i < nvec ? pr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int q = 0; q < W; q++) {
+                const float4* pr = reinterpret_cast<const float4*>(y + (size_t)min(p + q, S - 1) * slice + base);
+#pragma unroll
+                for (int k = 0; k < NV; k++) {
+                    const int i = threadIdx.x + k * blockDim.x;
+                    a[q][k] = i < nvec ? pr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             }
 #pragma unroll
-            for (int k = 0; k < LN_VEC; k++) { u[k].x += a[k].x; u[k].y += a[k].y; u[k].z += a[k].z; u[k].w += a[k].w; }
+            for (int q = 0; q < W; q++)
+                if (p + q < S) {
+#pragma unroll
+                    for (int k = 0; k < NV; k++) { u[k].x += a[q][k].x; u[k].y += a[q][k].y; u[k].z += a[q][k].z; u[k].w += a[q][k].w; }
+                }
         }
         const float2 st = reg_stats(u, nvec, D, peps, rms, scratch);
 #pragma unroll
-        for (int k = 0; k < LN_VEC; k++) {
+        for (int k = 0; k < NV; k++) {
             const int i = threadIdx.x + k * blockDim.x;
             if (i < nvec) {
                 const float4 g = ld_w4(pw, p_dt, i);
@@ -163,7 +173,7 @@ layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, int S, 
     if (out == nullptr) return;
     const float2 st = reg_stats(v, nvec, D, eps, rms, scratch);
 #pragma unroll
-    for (int k = 0; k < LN_VEC; k++) {
+    for (int k = 0; k < NV; k++) {
         const int i = threadIdx.x + k * blockDim.x;
         if (i < nvec) {
             const float4 g = ld_w4(w, w_dt, i);
@@ -201,15 +211,18 @@ GFB_API int gfb_layernorm(float* x, const float* y, int S, long slice, const voi
         // fewer threads with up to eight, so that more rows are resident per SM
         int per = R <= 256 ? 2 : LN_VEC;
         if ((D / 4 + per - 1) / per > 256) per = (D / 4 + 255) / 256;
+        per = per <= 2 ? 2 : per <= 4 ? 4 : LN_VEC;
         int vthreads = ((D / 4 + per - 1) / per + 31) / 32 * 32;
         if (vthreads < 64) vthreads = 64;
         if (vthreads > 256) vthreads = 256;
-        if (D / 4 <= LN_VEC * vthreads) {
-#define VGO(TO) e = gfb_launch(layernorm_vec_kernel<TO>, dim3(R), dim3(vthreads), 0, stream, x, y, S, (size_t)slice, pw, pb, p_dt, peps, \
-                               mult, w, b, w_dt, eps, (TO*)out, rows, D, rms)
-            if (out == nullptr || out_dt == GFB_F32) VGO(float);
-            else if (out_dt == GFB_BF16) VGO(__nv_bfloat16);
+        if (D / 4 <= per * vthreads) {
+#define VGO(TO, NV, W) e = gfb_launch(layernorm_vec_kernel<TO, NV, W>, dim3(R), dim3(vthreads), 0, stream, x, y, S, (size_t)slice, pw, pb, \
+                                      p_dt, peps, mult, w, b, w_dt, eps, (TO*)out, rows, D, rms)
+#define VPICK(TO) do { if (per == 2) VGO(TO, 2, 6); else if (per == 4) VGO(TO, 4, 3); else VGO(TO, 8, 1); } while (0)
+            if (out == nullptr || out_dt == GFB_F32) VPICK(float);
+            else if (out_dt == GFB_BF16) VPICK(__nv_bfloat16);
             else return gfb_fail("gfb_layernorm: unknown output type %d", out_dt);
+#undef VPICK
 #undef VGO
             return gfb_check(e, "gfb_layernorm (vector)");
         }

@@ -483,6 +483,76 @@ GFB_API long gfb_retention_scratch_floats(int n_tokens, int n_seqs, int max_q_le
     return ((long)(n_tokens + PC - 1) / PC + n_seqs) * H * dk * dv;
 }
 
+// ---- decode steps: one token per sequence ------------------------------------------------------------------
+// S <- decay S + k v^T and o = S^T q in one pass over the state, which is read and written once, straight from and to
+// memory: thread (ty, tx) walks over key dimensions ty, ty + 16, ... with 4 value columns in a 16-byte access, all of
+// a thread's loads independent of each other; the 16 partial outputs per column meet in shared memory and are added
+// in ascending order.  For value heads whose size is a multiple of 4.
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+retention_decode_kernel(const T* __restrict__ src, int width, int q_off, int k_off, int v_off, float* __restrict__ state,
+                        float* __restrict__ out, GfbBatch b, const float* __restrict__ table, int table_len, int rot_dims,
+                        int pairing, const float* __restrict__ decay, float k_scale, int H, int dk, int dv, int* status) {
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;                               // [dk] rotated q
+    float* ks = qs + dk;                            // [dk] rotated k times its factor
+    float* red = ks + dk;                           // [16][VS]
+    gfb_pdl_launch();
+    const int s = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * VS;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const float dec = decay[h];
+    const int slot = b.slots[s];
+    const int t = b.cu_seqlens[s];
+    gfb_pdl_wait();
+    const int pos = b.lengths[slot];
+    const T* row = src + (size_t)t * width;
+    const int half = rot_dims >> 1;
+    for (int u = tid; u < dk - half; u += THREADS) {
+        const T* qh = row + q_off + h * dk;
+        const T* kh = row + k_off + h * dk;
+        if (u < half) {
+            const float2 cs = rot_of(table, table_len, half, pos, u, (blockIdx.z == 0 && h == 0) ? status : nullptr, t);
+            const int i0 = pairing == 1 ? u : 2 * u, i1 = pairing == 1 ? u + half : 2 * u + 1;
+            const float qa = gfb_to_f32(qh[i0]), qb = gfb_to_f32(qh[i1]), ka = gfb_to_f32(kh[i0]), kb = gfb_to_f32(kh[i1]);
+            qs[i0] = qa * cs.x - qb * cs.y; qs[i1] = qb * cs.x + qa * cs.y;
+            ks[i0] = (ka * cs.x - kb * cs.y) * k_scale; ks[i1] = (kb * cs.x + ka * cs.y) * k_scale;
+        } else {
+            const int i0 = rot_dims + (u - half);
+            qs[i0] = gfb_to_f32(qh[i0]);
+            ks[i0] = gfb_to_f32(kh[i0]) * k_scale;
+        }
+    }
+    const int col = v0 + 4 * tx;
+    const bool live = col < dv;                     // dv % 4 == 0: a group of four columns is inside or outside
+    float vv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) vv[c] = gfb_to_f32(row[v_off + h * dv + col + c]);
+    }
+    __syncthreads();
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        float* Sg = state + ((size_t)slot * H + h) * dk * dv + col;
+#pragma unroll 4
+        for (int d = ty; d < dk; d += 16) {
+            float4 S4 = *reinterpret_cast<const float4*>(Sg + (size_t)d * dv);
+            const float kd = ks[d], qd = qs[d];
+            S4.x = dec * S4.x + kd * vv[0]; S4.y = dec * S4.y + kd * vv[1];
+            S4.z = dec * S4.z + kd * vv[2]; S4.w = dec * S4.w + kd * vv[3];
+            *reinterpret_cast<float4*>(Sg + (size_t)d * dv) = S4;
+            o[0] = fmaf(S4.x, qd, o[0]); o[1] = fmaf(S4.y, qd, o[1]); o[2] = fmaf(S4.z, qd, o[2]); o[3] = fmaf(S4.w, qd, o[3]);
+        }
+    }
+    *reinterpret_cast<float4*>(red + ty * VS + 4 * tx) = make_float4(o[0], o[1], o[2], o[3]);
+    __syncthreads();
+    if (tid < VS && v0 + tid < dv) {
+        float acc = 0.f;
+#pragma unroll
+        for (int g = 0; g < 16; g++) acc += red[g * VS + tid];
+        out[((size_t)t * H + h) * dv + v0 + tid] = acc;
+    }
+}
+
 static size_t retention_smem(int C, int dk) {
     return ((size_t)2 * C * (dk + 1) + (size_t)C * VS + (size_t)C * (C + 1) + (size_t)dk * VS + C + 1) * sizeof(float);
 }
@@ -532,6 +602,19 @@ GFB_API int gfb_retention(const void* src, int dt, int width, int q_off, int k_o
         return gfb_check(e, "gfb_retention (chunks side by side)");
     }
     dim3 grid(n_seqs, H, (dv + VS - 1) / VS);
+    if (max_q_len == 1 && n_tokens == n_seqs && dv % 4 == 0 && ((uintptr_t)state & 15) == 0 && (size_t)(2 * dk + 16 * VS) * 4 <= 48 * 1024) {
+        const size_t dsmem = (size_t)(2 * dk + 16 * VS) * sizeof(float);
+        cudaError_t e;
+        if (dt == GFB_BF16)
+            e = gfb_launch(retention_decode_kernel<__nv_bfloat16>, grid, dim3(THREADS), dsmem, stream, (const __nv_bfloat16*)src, width,
+                           q_off, k_off, v_off, state, out, b, table, table_len, rot_dims, pairing, decay, k_scale, H, dk, dv, status);
+        else if (dt == GFB_F32)
+            e = gfb_launch(retention_decode_kernel<float>, grid, dim3(THREADS), dsmem, stream, (const float*)src, width, q_off, k_off,
+                           v_off, state, out, b, table, table_len, rot_dims, pairing, decay, k_scale, H, dk, dv, status);
+        else
+            return gfb_fail("gfb_retention: unknown type %d", dt);
+        return gfb_check(e, "gfb_retention (decode)");
+    }
     // 64 tokens at a time where that fits beside the state slice; 16 for decode steps and very large heads
     const size_t limit = 220 * 1024;
     int C = (max_q_len > 16 && retention_smem(64, dk) <= limit) ? 64 : 16;

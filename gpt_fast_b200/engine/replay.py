@@ -35,10 +35,13 @@ from .step import Stepper
 class Replayer:
     def __init__(self, model, max_tokens: int, out_dir: Optional[str]):
         self.model = model
+        # max_tokens counts the tokens themselves; every live request may also leave a part of its last page unused,
+        # so there is one more page (and a slot) for each request that can be live at once, up to 1,024 of them
         page = DEFAULT_PAGE_SIZE
-        n_pages = -(-max_tokens // page)
-        self.cache = model.new_cache(max_tokens=n_pages * page, max_seqs=n_pages,
-                                     max_seq_len=min(n_pages * page, model.spec.max_position or n_pages * page))
+        longest = -(-max_tokens // page)
+        n_pages = longest + min(max_tokens, 1024)
+        self.cache = model.new_cache(max_tokens=n_pages * page, max_seqs=min(n_pages, longest + 1024),
+                                     max_seq_len=min(longest * page, model.spec.max_position or longest * page))
         self.stepper = Stepper(model, self.cache)
         self.slot_of: Dict[str, int] = {}
         self.out_dir = out_dir
@@ -95,6 +98,6 @@ def main(argv=None) -> int:
                     help="bfloat16: the kernels and precisions of serving; float32: everything in true 32-bit")
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="the most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+                    help="the most tokens live requests hold at any time (the cache adds room for part-filled pages)")
     a = ap.parse_args(argv)
     return run(a.model, a.dtype, a.out, a.max_tokens)

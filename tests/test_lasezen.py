@@ -229,6 +229,21 @@ def test_weights_round_trip_and_one_error(folders, tmp_path):
     assert e.value.missing == ["l1.mix.g"] and e.value.unexpected == ["l9.extra"] and e.value.wrong_shape[0][0] == "l0.mix.sink"
 
 
+def test_replay_has_room_for_many_short_requests(folders, backend):
+    """The replay's --max-tokens counts tokens, not pages: seven live requests of three tokens need seven pages."""
+    from gpt_fast_b200.engine.replay import Replayer
+    device, dtype = backend
+    folder = folders["lasezen-tiny-b"]
+    model = gf.load(folder, dtype=dtype, device=device)
+    reqs = {f"r{i}": tokens_of(model.vocab_size, 3, seed=40 + i) for i in range(7)}
+    rp = Replayer(model, 21, None)
+    rp.run_step({"step": 0, "entries": [{"id": k, "tokens": v[:2], "want": []} for k, v in reqs.items()], "end": []})
+    out = rp.run_step({"step": 1, "entries": [{"id": k, "tokens": v[2:], "want": [0]} for k, v in reqs.items()], "end": list(reqs)})
+    for i, v in enumerate(reqs.values()):
+        judge(torch.from_numpy(out[i:i + 1].copy()), folder, v, slice(2, 3), dtype, f"request {i}")
+    assert rp.cache.slots.n_free == rp.cache.n_slots
+
+
 # ---- the trace program as a user runs it ----------------------------------------------------------------------
 
 @pytest.mark.gpu

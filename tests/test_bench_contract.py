@@ -35,3 +35,24 @@ def test_reference_arm_prints_one_json_line():
 def test_reference_arm_imports_nothing_of_this_library():
     src = open(os.path.join(ROOT, "baseline", "reference_arm.py")).read()
     assert "gpt_fast_b200" not in src.replace("Nothing of gpt_fast_b200 is imported here", "")
+
+
+def test_design_option_pairs_a_llama_of_equal_size():
+    """`--design lasezen` sets the design beside a Llama decoder of the same width, depth and vocabulary and nearly the
+    same number of weights (counted from the two weight plans)."""
+    import math
+    sys.path.insert(0, ROOT)
+    import bench
+    import gpt_fast_b200 as gf
+    from gpt_fast_b200.config.registry import architecture_for
+
+    def weights(cfg):
+        arch = architecture_for(cfg)
+        return sum(math.prod(s.shape) for s in arch.weight_plan(arch.parse(cfg)).sources().values())
+    for name in ("lasezen-1b", "lasezen-7b"):
+        cfg = gf.config_from_name(name)
+        twin = bench.llama_twin(cfg)
+        assert twin["hidden_size"] == cfg["width"] and twin["num_hidden_layers"] == len(cfg["layers"]) and twin["vocab_size"] == cfg["vocab"]
+        assert abs(weights(twin) - weights(cfg)) < 0.05 * weights(cfg)
+    r = run("--design", "nothing-of-the-kind")
+    assert r.returncode == 2 and "no size table" in r.stdout

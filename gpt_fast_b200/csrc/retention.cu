@@ -248,7 +248,8 @@ __device__ __forceinline__ float2 rot_of(const float* table, int table_len, int 
     return make_float2(1.f, 0.f);
 }
 
-template <typename T>
+// VSX: value columns per block, 64 or 128 (a thread then owns two groups of four columns, 64 apart)
+template <typename T, int VSX>
 __global__ void __launch_bounds__(THREADS)
 chunk_state_kernel(const T* __restrict__ src, int width, int k_off, int v_off, float* __restrict__ U, GfbBatch b,
                    const float* __restrict__ table, int table_len, int rot_dims, int pairing, const float* __restrict__ decay,
@@ -256,10 +257,10 @@ chunk_state_kernel(const T* __restrict__ src, int width, int k_off, int v_off, f
     extern __shared__ __align__(16) float smem[];
     const int dk4 = (dk + 3) & ~3;
     float* Kc = smem;                               // [PC][dk4]: rotated k times its factor and decay^(n-1-j)
-    float* Vs = Kc + (size_t)PC * dk4;              // [PC][VS]
-    float* pw = Vs + (size_t)PC * VS;               // [PC+1]
+    float* Vs = Kc + (size_t)PC * dk4;              // [PC][VSX]
+    float* pw = Vs + (size_t)PC * VSX;               // [PC+1]
     gfb_pdl_launch();
-    const int w = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * VS;
+    const int w = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * VSX;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const float dec = decay[h];
     for (int n = tid; n <= PC; n += THREADS) pw[n] = (float)pow((double)dec, (double)n);
@@ -289,37 +290,46 @@ chunk_state_kernel(const T* __restrict__ src, int width, int k_off, int v_off, f
             kd[i0] = i0 < dk ? gfb_to_f32(kh[i0]) * f : 0.f;
         }
     }
-    for (int e = tid; e < PC * VS; e += THREADS) {
-        const int j = e / VS, v = e - j * VS;
+    for (int e = tid; e < PC * VSX; e += THREADS) {
+        const int j = e / VSX, v = e - j * VSX;
         Vs[e] = (j < c.n && v0 + v < dv) ? gfb_to_f32(src[(size_t)(c.t0 + j) * width + v_off + h * dv + v0 + v]) : 0.f;
     }
     __syncthreads();
     float* Ug = U + ((size_t)w * H + h) * dk * dv;
     for (int d0 = 0; d0 < dk; d0 += 64) {
         if (d0 + 4 * ty >= dk4) continue;
-        float acc[4][4];
+        constexpr int NG = VSX / 64;
+        float acc[NG][4][4];
 #pragma unroll
-        for (int r = 0; r < 4; r++)
-#pragma unroll
-            for (int cc = 0; cc < 4; cc++) acc[r][cc] = 0.f;
-        for (int j = 0; j < c.n; j++) {
-            const float4 k4 = *reinterpret_cast<const float4*>(Kc + (size_t)j * dk4 + d0 + 4 * ty);
-            const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * VS + 4 * tx);
-            const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+        for (int g = 0; g < NG; g++)
 #pragma unroll
             for (int r = 0; r < 4; r++)
 #pragma unroll
-                for (int cc = 0; cc < 4; cc++) acc[r][cc] = fmaf(kk[r], vv[cc], acc[r][cc]);
+                for (int cc = 0; cc < 4; cc++) acc[g][r][cc] = 0.f;
+        for (int j = 0; j < c.n; j++) {
+            const float4 k4 = *reinterpret_cast<const float4*>(Kc + (size_t)j * dk4 + d0 + 4 * ty);
+            const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+            for (int g = 0; g < NG; g++) {
+                const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * VSX + 64 * g + 4 * tx);
+                const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int cc = 0; cc < 4; cc++) acc[g][r][cc] = fmaf(kk[r], vv[cc], acc[g][r][cc]);
+            }
         }
 #pragma unroll
         for (int r = 0; r < 4; r++) {
             const int d = d0 + 4 * ty + r;
             if (d >= dk) continue;
 #pragma unroll
-            for (int cc = 0; cc < 4; cc++) {
-                const int v = v0 + 4 * tx + cc;
-                if (v < dv) Ug[(size_t)d * dv + v] = acc[r][cc];
-            }
+            for (int g = 0; g < NG; g++)
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) {
+                    const int v = v0 + 64 * g + 4 * tx + cc;
+                    if (v < dv) Ug[(size_t)d * dv + v] = acc[g][r][cc];
+                }
         }
     }
 }
@@ -352,7 +362,8 @@ chunk_scan_kernel(float* __restrict__ U, float* __restrict__ state, GfbBatch b, 
     *Sg = S;
 }
 
-template <typename T>
+// VSX: value columns per block, 64 or 128 (a thread then owns two groups of four columns, 64 apart)
+template <typename T, int VSX>
 __global__ void __launch_bounds__(THREADS)
 chunk_out_kernel(const T* __restrict__ src, int width, int q_off, int k_off, int v_off, const float* __restrict__ U,
                  float* __restrict__ out, GfbBatch b, const float* __restrict__ table, int table_len, int rot_dims, int pairing,
@@ -360,12 +371,12 @@ chunk_out_kernel(const T* __restrict__ src, int width, int q_off, int k_off, int
     extern __shared__ __align__(16) float smem[];
     float* Qt = smem;                               // [dk][CP]: rotated q, token fastest
     float* Kt = Qt + (size_t)dk * CP;               // [dk][CP]: rotated k times its factor
-    float* Vs = Kt + (size_t)dk * CP;               // [PC][VS]
-    float* At = Vs + (size_t)PC * VS;               // [PC][CP]: At[j][i] = (q_i . k_j) decay^(i-j) for j <= i
-    float* Ss = At + (size_t)PC * CP;               // [dk][VS]: the state before this chunk
-    float* pw = Ss + (size_t)dk * VS;               // [PC+1]
+    float* Vs = Kt + (size_t)dk * CP;               // [PC][VSX]
+    float* At = Vs + (size_t)PC * VSX;               // [PC][CP]: At[j][i] = (q_i . k_j) decay^(i-j) for j <= i
+    float* Ss = At + (size_t)PC * CP;               // [dk][VSX]: the state before this chunk
+    float* pw = Ss + (size_t)dk * VSX;               // [PC+1]
     gfb_pdl_launch();
-    const int w = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * VS;
+    const int w = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * VSX;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const float dec = decay[h];
     for (int n = tid; n <= PC; n += THREADS) pw[n] = (float)pow((double)dec, (double)n);
@@ -396,13 +407,13 @@ chunk_out_kernel(const T* __restrict__ src, int width, int q_off, int k_off, int
             Kt[(size_t)i0 * CP + i] = live ? gfb_to_f32(kh[i0]) * k_scale : 0.f;
         }
     }
-    for (int e = tid; e < PC * VS; e += THREADS) {
-        const int j = e / VS, v = e - j * VS;
+    for (int e = tid; e < PC * VSX; e += THREADS) {
+        const int j = e / VSX, v = e - j * VSX;
         Vs[e] = (j < c.n && v0 + v < dv) ? gfb_to_f32(src[(size_t)(c.t0 + j) * width + v_off + h * dv + v0 + v]) : 0.f;
     }
     const float* Ug = U + ((size_t)w * H + h) * dk * dv;
-    for (int e = tid; e < dk * VS; e += THREADS) {
-        const int d = e / VS, v = e - d * VS;
+    for (int e = tid; e < dk * VSX; e += THREADS) {
+        const int d = e / VSX, v = e - d * VSX;
         Ss[e] = (v0 + v < dv) ? Ug[(size_t)d * dv + v0 + v] : 0.f;
     }
     __syncthreads();
@@ -437,45 +448,58 @@ chunk_out_kernel(const T* __restrict__ src, int width, int q_off, int k_off, int
     }
     __syncthreads();
     if (4 * ty < c.n) {
-        float acc[4][4], carry[4][4];
+        constexpr int NG = VSX / 64;
+        float acc[NG][4][4], carry[NG][4][4];
 #pragma unroll
-        for (int r = 0; r < 4; r++)
+        for (int g = 0; g < NG; g++)
 #pragma unroll
-            for (int cc = 0; cc < 4; cc++) { acc[r][cc] = 0.f; carry[r][cc] = 0.f; }
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) { acc[g][r][cc] = 0.f; carry[g][r][cc] = 0.f; }
         const int jmax = min(c.n, 4 * ty + 4);           // A[i][j] = 0 beyond the row's own position
         for (int j = 0; j < jmax; j++) {
             const float4 a4 = *reinterpret_cast<const float4*>(At + (size_t)j * CP + 4 * ty);
-            const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * VS + 4 * tx);
-            const float aa[4] = {a4.x, a4.y, a4.z, a4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+            const float aa[4] = {a4.x, a4.y, a4.z, a4.w};
 #pragma unroll
-            for (int r = 0; r < 4; r++)
+            for (int g = 0; g < NG; g++) {
+                const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * VSX + 64 * g + 4 * tx);
+                const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
-                for (int cc = 0; cc < 4; cc++) acc[r][cc] = fmaf(aa[r], vv[cc], acc[r][cc]);
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int cc = 0; cc < 4; cc++) acc[g][r][cc] = fmaf(aa[r], vv[cc], acc[g][r][cc]);
+            }
         }
         for (int d = 0; d < dk; d++) {
             const float4 q4 = *reinterpret_cast<const float4*>(Qt + (size_t)d * CP + 4 * ty);
-            const float4 s4 = *reinterpret_cast<const float4*>(Ss + d * VS + 4 * tx);
-            const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+            const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-            for (int r = 0; r < 4; r++)
+            for (int g = 0; g < NG; g++) {
+                const float4 s4 = *reinterpret_cast<const float4*>(Ss + d * VSX + 64 * g + 4 * tx);
+                const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
-                for (int cc = 0; cc < 4; cc++) carry[r][cc] = fmaf(qq[r], ss[cc], carry[r][cc]);
+                for (int r = 0; r < 4; r++)
+#pragma unroll
+                    for (int cc = 0; cc < 4; cc++) carry[g][r][cc] = fmaf(qq[r], ss[cc], carry[g][r][cc]);
+            }
         }
 #pragma unroll
         for (int r = 0; r < 4; r++) {
             const int i = 4 * ty + r;
             if (i >= c.n) continue;
 #pragma unroll
-            for (int cc = 0; cc < 4; cc++) {
-                const int v = v0 + 4 * tx + cc;
-                if (v < dv) out[((size_t)(c.t0 + i) * H + h) * dv + v] = acc[r][cc] + pw[i + 1] * carry[r][cc];
-            }
+            for (int g = 0; g < NG; g++)
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) {
+                    const int v = v0 + 64 * g + 4 * tx + cc;
+                    if (v < dv) out[((size_t)(c.t0 + i) * H + h) * dv + v] = acc[g][r][cc] + pw[i + 1] * carry[g][r][cc];
+                }
         }
     }
 }
 
-static size_t chunk_state_smem(int dk) { return ((size_t)PC * ((dk + 3) & ~3) + (size_t)PC * VS + PC + 1) * sizeof(float); }
-static size_t chunk_out_smem(int dk) { return ((size_t)2 * dk * CP + (size_t)PC * VS + (size_t)PC * CP + (size_t)dk * VS + PC + 1) * sizeof(float); }
+static size_t chunk_state_smem(int dk, int vs = VS) { return ((size_t)PC * ((dk + 3) & ~3) + (size_t)PC * vs + PC + 1) * sizeof(float); }
+static size_t chunk_out_smem(int dk, int vs = VS) { return ((size_t)2 * dk * CP + (size_t)PC * vs + (size_t)PC * CP + (size_t)dk * vs + PC + 1) * sizeof(float); }
 
 // Floats of scratch the three-launch form needs for a step of n_tokens tokens in n_seqs sequences (0: it does not apply).
 GFB_API long gfb_retention_scratch_floats(int n_tokens, int n_seqs, int max_q_len, int H, int dk, int dv) {
@@ -575,28 +599,34 @@ GFB_API int gfb_retention(const void* src, int dt, int width, int q_off, int k_o
         // prompts of several chunks: the chunks side by side, in three launches
         const int n_chunks = (n_tokens + PC - 1) / PC + n_seqs;       // an upper bound; surplus blocks find no work
         if (n_chunks > 0x7fffffff / 2 || n_seqs > 65535) return gfb_fail("gfb_retention: too many chunks or sequences");
-        dim3 cgrid(n_chunks, H, (dv + VS - 1) / VS);
-        const size_t s1 = chunk_state_smem(dk), s3 = chunk_out_smem(dk);
+        // 128 value columns per block where the head has them and the tiles fit: the score tile is computed once per 128
+        // columns and every 16-byte load of q, k or a score feeds 32 FMAs instead of 16
+        const bool wide = dv >= 128 && chunk_out_smem(dk, 128) <= 220 * 1024;
+        const int vs = wide ? 128 : VS;
+        dim3 cgrid(n_chunks, H, (dv + vs - 1) / vs);
+        const size_t s1 = chunk_state_smem(dk, vs), s3 = chunk_out_smem(dk, vs);
         cudaError_t e;
-#define GO3(T)                                                                                                         \
+#define GO3(T, V)                                                                                                         \
         do {                                                                                                           \
             static bool configured = false;                                                                            \
             if (!configured) {                                                                                         \
-                cudaFuncSetAttribute(chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);  \
-                cudaFuncSetAttribute(chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);    \
+                cudaFuncSetAttribute(chunk_state_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);  \
+                cudaFuncSetAttribute(chunk_out_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);    \
                 configured = true;                                                                                     \
             }                                                                                                          \
-            e = gfb_launch(chunk_state_kernel<T>, cgrid, dim3(THREADS), s1, stream, (const T*)src, width, k_off, v_off, scratch, b, \
+            e = gfb_launch(chunk_state_kernel<T, V>, cgrid, dim3(THREADS), s1, stream, (const T*)src, width, k_off, v_off, scratch, b, \
                            table, table_len, rot_dims, pairing, decay, k_scale, H, dk, dv, status);                    \
             if (e == cudaSuccess)                                                                                      \
                 e = gfb_launch(chunk_scan_kernel, dim3((unsigned)(((size_t)dk * dv + 255) / 256), n_seqs, H), dim3(256), 0, stream, \
                                scratch, state, b, decay, H, dk, dv);                                                   \
             if (e == cudaSuccess)                                                                                      \
-                e = gfb_launch(chunk_out_kernel<T>, cgrid, dim3(THREADS), s3, stream, (const T*)src, width, q_off, k_off, v_off, \
+                e = gfb_launch(chunk_out_kernel<T, V>, cgrid, dim3(THREADS), s3, stream, (const T*)src, width, q_off, k_off, v_off, \
                                (const float*)scratch, out, b, table, table_len, rot_dims, pairing, decay, k_scale, H, dk, dv, status); \
         } while (0)
-        if (dt == GFB_BF16) GO3(__nv_bfloat16);
-        else if (dt == GFB_F32) GO3(float);
+        if (dt == GFB_BF16 && wide) GO3(__nv_bfloat16, 128);
+        else if (dt == GFB_BF16) GO3(__nv_bfloat16, 64);
+        else if (dt == GFB_F32 && wide) GO3(float, 128);
+        else if (dt == GFB_F32) GO3(float, 64);
         else return gfb_fail("gfb_retention: unknown type %d", dt);
 #undef GO3
         return gfb_check(e, "gfb_retention (chunks side by side)");

@@ -9,11 +9,13 @@ import torch
 class KVNeed:
     """Keys and values per token: n_kv heads of head_dim.  `window` (or None)
     is how many of the latest positions the mixer ever reads.  `v_head_dim`
-    (or None: head_dim) is the values' head size where it differs from the keys'."""
+    (or None: head_dim) is the values' head size where it differs from the keys'.
+    `values=False`: the mixer reads its values out of the key rows, so no value storage is made."""
     n_kv: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    values: bool = True
 
 
 @dataclass(frozen=True)

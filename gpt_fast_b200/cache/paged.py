@@ -38,7 +38,8 @@ class _KVGroup:
         self.index = {e: i for i, e in enumerate(entries)}
         shape = (len(entries), n_pages, need.n_kv, page_size, need.head_dim)
         self.k_pool = torch.zeros(shape, dtype=dtype, device=device)
-        self.v_pool = torch.zeros(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
+        v_dim = (need.v_head_dim or need.head_dim) if need.values else 0
+        self.v_pool = torch.zeros(shape[:-1] + (v_dim,), dtype=dtype, device=device)
         self.pages = FreeList(n_pages, "page")
         self.table_host = torch.full((n_slots, max_pages), -1, dtype=torch.int32)
         self.table = self.table_host.to(device)
@@ -177,5 +178,5 @@ class Cache:
         return n + sum(g.data.numel() * g.data.element_size() for g in self.state_groups)
 
     def kv_bytes_per_token(self) -> int:
-        return sum(len(g.entries) * g.need.n_kv * (g.need.head_dim + (g.need.v_head_dim or g.need.head_dim)) * g.k_pool.element_size()
+        return sum(len(g.entries) * g.need.n_kv * (g.need.head_dim + g.v_pool.shape[-1]) * g.k_pool.element_size()
                    for g in self.kv_groups)

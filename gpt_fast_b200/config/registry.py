@@ -24,12 +24,15 @@ class Architecture:
     parse:        config.json dict -> typed configuration
     build_spec:   typed configuration -> config.spec.ModelSpec
     weight_plan:  typed configuration -> weights.plan.WeightPlan (tensor names)
+    shapes_from_checkpoint: some sizes of the model are given only by tensor shapes; build_spec and weight_plan then
+                  take a second argument, the checkpoint's {tensor name: shape} (None when there is no checkpoint)
     """
     name: str
     parse: Callable[[Dict[str, Any]], Any]
     build_spec: Callable[[Any], Any]
     weight_plan: Callable[[Any], Any]
     aliases: tuple = ()
+    shapes_from_checkpoint: bool = False
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}

@@ -8,8 +8,8 @@
 // scaled by `scale`; softmax is 32-bit.  Options that other mixers use: `chunk` (a query
 // sees only keys of its own block of `chunk` positions, blocks counted from
 // position 0 of the sequence), `sink` (one number per query head whose
-// exponential joins the softmax denominator without a value) and a value head
-// size `dv` of its own.
+// exponential joins the softmax denominator without a value), a value head
+// size `dv` of its own, and values that are the leading part of the key rows.
 //
 // One block per (token, query head).  Keys are visited in chunks of 128 that
 // start at multiples of 128 of the ABSOLUTE position, with an online softmax
@@ -27,7 +27,7 @@ constexpr int MAX_DPT = 4;      // head_dim <= CHUNK * MAX_DPT
 template <typename T>
 __global__ void __launch_bounds__(CHUNK)
 attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedKV kv, GfbBatch b,
-                         int H, int G, int d, int dv, float scale, int window, int chunk,
+                         int H, int G, int d, int dv, int v_row, float scale, int window, int chunk,
                          const float* __restrict__ sink, int* status) {
     extern __shared__ float smem[];
     float* qs = smem;              // [d]
@@ -49,8 +49,8 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedK
     if (window > 0 && pos - window + 1 > 0) lo = pos - window + 1;
     if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
     const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
-    const size_t head_off = (size_t)g * kv.page_size * d, v_head_off = (size_t)g * kv.page_size * dv;
-    const size_t page_stride = (size_t)G * kv.page_size * d, v_page_stride = (size_t)G * kv.page_size * dv;
+    const size_t head_off = (size_t)g * kv.page_size * d, v_head_off = (size_t)g * kv.page_size * v_row;
+    const size_t page_stride = (size_t)G * kv.page_size * d, v_page_stride = (size_t)G * kv.page_size * v_row;
 
     float m_run = -INFINITY, l_run = 0.f;
     float acc[MAX_DPT];
@@ -97,7 +97,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, GfbPagedK
                     int pg = page_of[jj];
                     if (pg < 0) continue;
                     const T* vrow = (const T*)kv.v_pool + (size_t)pg * v_page_stride + v_head_off
-                                    + (size_t)((c0 + jj) % kv.page_size) * dv;
+                                    + (size_t)((c0 + jj) % kv.page_size) * v_row;
                     a = fmaf(ps[jj], gfb_to_f32(vrow[dim]), a);
                 }
                 acc[r] = a;
@@ -127,23 +127,27 @@ GFB_API int gfb_attention_generic(const void* q, void* out, int dt,
                                   int n_pages,
                                   const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths,
                                   int n_seqs, int n_tokens, int H, int G, int d, int dv, float scale, int window,
-                                  int chunk, const float* sink, int* status, cudaStream_t stream) {
+                                  int chunk, const float* sink, int values_in_keys, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dv <= 0) dv = d;
     if (dv > CHUNK * MAX_DPT) return gfb_fail("gfb_attention_generic: value head size %d exceeds %d", dv, CHUNK * MAX_DPT);
     if (G <= 0 || H % G) return gfb_fail("gfb_attention_generic: %d heads do not divide into %d groups", H, G);
     if (H > 65535) return gfb_fail("gfb_attention_generic: %d heads exceed the grid limit", H);
-    GfbPagedKV kv{k_pool, v_pool, page_table, max_pages, page_size, n_pages};
+    // values_in_keys: a value is the first dv dimensions of its key row (a latent shared by keys and values), so
+    // the value pool is the key pool read with the keys' row stride
+    if (values_in_keys && dv > d) return gfb_fail("gfb_attention_generic: values of %d dimensions inside keys of %d", dv, d);
+    const int v_row = values_in_keys ? d : dv;
+    GfbPagedKV kv{k_pool, values_in_keys ? k_pool : v_pool, page_table, max_pages, page_size, n_pages};
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     dim3 grid(n_tokens, H);
     size_t smem = (size_t)(d + CHUNK) * sizeof(float);
     cudaError_t e;
     if (dt == GFB_BF16)
         e = gfb_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(CHUNK), smem, stream,
-                       (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b, H, G, d, dv, scale, window, chunk, sink, status);
+                       (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, b, H, G, d, dv, v_row, scale, window, chunk, sink, status);
     else if (dt == GFB_F32)
         e = gfb_launch(attention_generic_kernel<float>, grid, dim3(CHUNK), smem, stream,
-                       (const float*)q, (float*)out, kv, b, H, G, d, dv, scale, window, chunk, sink, status);
+                       (const float*)q, (float*)out, kv, b, H, G, d, dv, v_row, scale, window, chunk, sink, status);
     else
         return gfb_fail("gfb_attention_generic: unknown type %d", dt);
     return gfb_check(e, "gfb_attention_generic");

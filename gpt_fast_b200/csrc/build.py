@@ -35,6 +35,9 @@ LIBRARIES = {
     "qkv_prepare": (["qkv_prepare.cu"], [], []),
     "retention": (["retention.cu"], [], []),
     "elementwise": (["elementwise.cu"], [], []),
+    "embedding": (["embedding.cu"], [], []),
+    "latent": (["latent.cu"], [], []),
+    "recurrent": (["recurrent.cu"], [], []),
 }
 HEADERS = ["common.cuh", "attn_decode_noalloc.h"]
 
@@ -66,7 +69,7 @@ def build_dir() -> str:
             continue
         try:
             os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".probe-{os.getpid()}")
+            probe = os.path.join(d, f".probe-{os.getpid()}-{threading.get_ident()}")
             with open(probe, "w"):
                 pass
             os.remove(probe)

@@ -296,21 +296,22 @@ GFB_API int gfb_add_partials(float* x, const float* pending, int S, long n, cuda
 // ------------------------------------------------------------- rotary table --
 // table[p][i] = (cos, sin)(p * inv_freq[i]); the angle is the 32-bit product,
 // cosf/sinf are the accurate versions (this file is built without fast-math).
-__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float* __restrict__ table, int P, int half) {
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, float* __restrict__ table, int P, int half, float amplitude) {
     gfb_pdl_launch();
     gfb_pdl_wait();
     int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= P * half) return;
     int p = idx / half, i = idx - p * half;
     float ang = (float)p * inv_freq[i];
-    table[2 * (size_t)idx] = cosf(ang);
-    table[2 * (size_t)idx + 1] = sinf(ang);
+    table[2 * (size_t)idx] = cosf(ang) * amplitude;            // amplitude 1 changes no bit
+    table[2 * (size_t)idx + 1] = sinf(ang) * amplitude;
 }
 
-GFB_API int gfb_rope_table(const float* inv_freq, float* table, int P, int half, cudaStream_t stream) {
+// amplitude: a factor on both cos and sin (1 for plain rotation; a length-scaling rule may ask for another).
+GFB_API int gfb_rope_table(const float* inv_freq, float* table, int P, int half, float amplitude, cudaStream_t stream) {
     long total = (long)P * half;
     if (total <= 0) return 0;
-    cudaError_t e = gfb_launch(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, inv_freq, table, P, half);
+    cudaError_t e = gfb_launch(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, inv_freq, table, P, half, amplitude);
     return gfb_check(e, "gfb_rope_table");
 }
 

@@ -1,11 +1,11 @@
 // Unary activations over a tensor, in place or to another tensor of the same type: the exact
-// (erf) GELU, the tanh form of GELU, and SiLU.  Arithmetic is 32-bit.  Products apply the same
+// (erf) GELU, the tanh form of GELU, SiLU, and the square of ReLU.  Arithmetic is 32-bit.  Products apply the same
 // functions in their epilogue where they can; this kernel serves the shapes that cannot.
 #include "common.cuh"
 
 GFB_DEFINE_LAST_ERROR()
 
-enum { ACT_GELU = 4, ACT_GELU_TANH = 5, ACT_SILU = 6 };     // numbered as the product kernels' epilogues
+enum { ACT_GELU = 4, ACT_GELU_TANH = 5, ACT_SILU = 6, ACT_RELU2 = 7 };     // numbered as the product kernels' epilogues
 
 template <typename T>
 __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n, int kind) {
@@ -17,13 +17,14 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, 
     float r;
     if (kind == ACT_GELU) r = 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
     else if (kind == ACT_GELU_TANH) r = 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    else if (kind == ACT_RELU2) { const float p = fmaxf(z, 0.f); r = p * p; }
     else r = z / (1.0f + expf(-z));
     out[i] = gfb_from_f32<T>(r);
 }
 
 GFB_API int gfb_activation(const void* x, void* out, int dt, long n, int kind, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (kind != ACT_GELU && kind != ACT_GELU_TANH && kind != ACT_SILU) return gfb_fail("gfb_activation: unknown activation %d", kind);
+    if (kind != ACT_GELU && kind != ACT_GELU_TANH && kind != ACT_SILU && kind != ACT_RELU2) return gfb_fail("gfb_activation: unknown activation %d", kind);
     const unsigned blocks = (unsigned)((n + 255) / 256);
     cudaError_t e;
     if (dt == GFB_BF16) e = gfb_launch(activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, (size_t)n, kind);

@@ -15,13 +15,14 @@
 
 GFB_DEFINE_LAST_ERROR()
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_GELU = 4, EPI_GELU_TANH = 5, EPI_SILU = 6 };   // 3: the tensor-core kernel's partial sums
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_GELU = 4, EPI_GELU_TANH = 5, EPI_SILU = 6, EPI_RELU2 = 7 };   // 3: the tensor-core kernel's partial sums
 
 template <int EPI>
 __device__ __forceinline__ float unary(float z) {
     if (EPI == EPI_GELU) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
     if (EPI == EPI_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
     if (EPI == EPI_SILU) return z / (1.0f + expf(-z));
+    if (EPI == EPI_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
     return z;
 }
 
@@ -108,6 +109,7 @@ static int launch(const void* A, const void* W, void* C, int M, int N, int K, in
     else if (epi == EPI_GELU) GO(EPI_GELU);
     else if (epi == EPI_GELU_TANH) GO(EPI_GELU_TANH);
     else if (epi == EPI_SILU) GO(EPI_SILU);
+    else if (epi == EPI_RELU2) GO(EPI_RELU2);
     else return gfb_fail("gfb_gemm_simt: unknown epilogue %d", epi);
 #undef GO
     return gfb_check(e, "gfb_gemm_simt");

@@ -27,12 +27,13 @@
 
 GFB_DEFINE_LAST_ERROR()
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_GELU = 4 };   // GELU: store gelu(acc), the exact (erf) form, as bfloat16
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_GELU = 4, EPI_RELU2 = 7 };   // GELU: store gelu(acc), the exact (erf) form, as bfloat16; RELU2: store max(acc, 0)^2
 
 // what a storing epilogue does to an accumulator value before it rounds it
 template <int EPI>
 __device__ __forceinline__ float fin(float x) {
     if (EPI == EPI_GELU) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+    if (EPI == EPI_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
     return x;
 }
 
@@ -1129,6 +1130,7 @@ int dispatch_epi(int epi, int out_dt, const CUtensorMap& mx, const CUtensorMap& 
     if (epi == EPI_ADD) GO(EPI_ADD, float);
     if (epi == EPI_SWIGLU) GO(EPI_SWIGLU, bf16);
     if (epi == EPI_GELU && out_dt == GFB_BF16) GO(EPI_GELU, bf16);
+    if (epi == EPI_RELU2 && out_dt == GFB_BF16) GO(EPI_RELU2, bf16);
     if (epi == EPI_STORE && out_dt == GFB_F32) GO(EPI_STORE, float);
     if (epi == EPI_STORE && out_dt == GFB_BF16) GO(EPI_STORE, bf16);
 #undef GO
@@ -1150,7 +1152,7 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
     if (K <= 0 || K % 8) return gfb_fail("gfb_gemm_tc: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
     if (N % 8) return gfb_fail("gfb_gemm_tc: N = %d must be a multiple of 8", N);
     if (epi == EPI_SWIGLU && N % 16) return gfb_fail("gfb_gemm_tc: SwiGLU needs N %% 16 == 0, got %d", N);
-    if (epi == EPI_GELU && out_dt != GFB_BF16) return gfb_fail("gfb_gemm_tc: the GELU epilogue stores bfloat16");
+    if ((epi == EPI_GELU || epi == EPI_RELU2) && out_dt != GFB_BF16) return gfb_fail("gfb_gemm_tc: the GELU and squared-ReLU epilogues store bfloat16");
     if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)out) & 15) return gfb_fail("gfb_gemm_tc: operands must be 16-byte aligned");
     if (stages < 2 || stages > MAX_STAGES) return gfb_fail("gfb_gemm_tc: stages = %d out of range", stages);
     if (bn < 512 && smem_bytes(bn, stages) > 227 * 1024) return gfb_fail("gfb_gemm_tc: %d stages of a %d-column tile exceed shared memory", stages, bn);
@@ -1188,6 +1190,7 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
         if (epi == EPI_ADD) return launch_pair<EPI_ADD, float>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
         if (epi == EPI_SWIGLU) return launch_pair<EPI_SWIGLU, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
         if (epi == EPI_GELU) return launch_pair<EPI_GELU, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
+        if (epi == EPI_RELU2) return launch_pair<EPI_RELU2, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
         if (out_dt == GFB_F32) return launch_pair<EPI_STORE, float>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
         return launch_pair<EPI_STORE, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count2, status, stream);
     }
@@ -1207,6 +1210,7 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
         if (epi == EPI_ADD) return launch_persistent<EPI_ADD, float>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
         if (epi == EPI_SWIGLU) return launch_persistent<EPI_SWIGLU, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
         if (epi == EPI_GELU) return launch_persistent<EPI_GELU, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
+        if (epi == EPI_RELU2) return launch_persistent<EPI_RELU2, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
         if (out_dt == GFB_F32) return launch_persistent<EPI_STORE, float>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
         return launch_persistent<EPI_STORE, bf16>(mx, my2, out, M, N, K, ldo, st, sm_count, status, stream);
     }
@@ -1229,6 +1233,7 @@ GFB_API int gfb_gemm_tc(const void* A, const void* W, void* out, int out_dt, int
         if (epi == EPI_ADD) RED(EPI_ADD, float);
         else if (epi == EPI_SWIGLU) RED(EPI_SWIGLU, bf16);
         else if (epi == EPI_GELU) RED(EPI_GELU, bf16);
+        else if (epi == EPI_RELU2) RED(EPI_RELU2, bf16);
         else if (out_dt == GFB_F32) RED(EPI_STORE, float);
         else RED(EPI_STORE, bf16);
 #undef RED

@@ -55,7 +55,7 @@ __global__ void layernorm_kernel(float* __restrict__ x, const float* __restrict_
         __syncthreads();
         for (int i = threadIdx.x; i < D; i += blockDim.x) {
             float n = (row[i] - st.x) * st.y * ld_w(pw, p_dt, i);
-            if (!rms) n += ld_w(pb, p_dt, i);
+            if (!rms && pb != nullptr) n += ld_w(pb, p_dt, i);
             const float v = x[base + i] + mult * n;
             x[base + i] = v;
             row[i] = v;
@@ -69,7 +69,7 @@ __global__ void layernorm_kernel(float* __restrict__ x, const float* __restrict_
     TO* o = out + (size_t)r * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
         float n = (row[i] - st.x) * st.y * ld_w(w, w_dt, i);
-        if (!rms) n += ld_w(b, w_dt, i);
+        if (!rms && b != nullptr) n += ld_w(b, w_dt, i);
         o[i] = gfb_from_f32<TO>(n);
     }
 }
@@ -164,7 +164,7 @@ layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, int S, 
                 const float4 g = ld_w4(pw, p_dt, i);
                 float4 n = make_float4((u[k].x - st.x) * st.y * g.x, (u[k].y - st.x) * st.y * g.y,
                                        (u[k].z - st.x) * st.y * g.z, (u[k].w - st.x) * st.y * g.w);
-                if (!rms) { const float4 c = ld_w4(pb, p_dt, i); n.x += c.x; n.y += c.y; n.z += c.z; n.w += c.w; }
+                if (!rms && pb != nullptr) { const float4 c = ld_w4(pb, p_dt, i); n.x += c.x; n.y += c.y; n.z += c.z; n.w += c.w; }
                 v[k].x += mult * n.x; v[k].y += mult * n.y; v[k].z += mult * n.z; v[k].w += mult * n.w;
                 xr[i] = v[k];
             }
@@ -179,7 +179,7 @@ layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ y, int S, 
             const float4 g = ld_w4(w, w_dt, i);
             float4 n = make_float4((v[k].x - st.x) * st.y * g.x, (v[k].y - st.x) * st.y * g.y,
                                    (v[k].z - st.x) * st.y * g.z, (v[k].w - st.x) * st.y * g.w);
-            if (!rms) { const float4 c = ld_w4(b, w_dt, i); n.x += c.x; n.y += c.y; n.z += c.z; n.w += c.w; }
+            if (!rms && b != nullptr) { const float4 c = ld_w4(b, w_dt, i); n.x += c.x; n.y += c.y; n.z += c.z; n.w += c.w; }
             TO* o = out + (size_t)r * D + 4 * i;
             if (sizeof(TO) == 4) {
                 *reinterpret_cast<float4*>(o) = n;
@@ -244,4 +244,103 @@ GFB_API int gfb_layernorm(float* x, const float* y, int S, long slice, const voi
     else return gfb_fail("gfb_layernorm: unknown output type %d", out_dt);
 #undef GO
     return gfb_check(e, "gfb_layernorm");
+}
+
+// ---------------------------------------------------------------- one row, several norms ---------
+// For blocks whose sublayers all read the SAME normed row (parallel blocks): per row
+//   (1) x[row] += sum_b s_b * y_b[row]      up to two branches, each a 32-bit tensor or the partial sums of a
+//                                           product split over K (added in ascending order), each with a
+//                                           per-column factor s_b (or none); written back
+//   (2) out_k[r] = (x - mean) / sqrt(var + eps_k) * w_k      up to two outputs from ONE mean and variance
+// The row sits in shared memory; statistics are 32-bit, the variance is the mean of squared deviations.
+struct LnBranch {
+    const float* y;      // [max(S, 1)][T][D], or null
+    int S;
+    const void* scale;   // [D] of type scale_dt, or null
+};
+struct LnOut {
+    const void* w;       // [D] of type w_dt
+    float eps;
+    void* out;           // [R][D], or null
+};
+
+template <typename TO>
+__global__ void layernorm_multi_kernel(float* __restrict__ x, LnBranch b0, LnBranch b1, int scale_dt, size_t slice,
+                                       LnOut o0, LnOut o1, int w_dt, const int* __restrict__ rows, int D, int rms) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int r = blockIdx.x;
+    const size_t base = (size_t)(rows ? rows[r] : r) * D;
+    const bool sums = b0.y != nullptr || b1.y != nullptr;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = x[base + i];
+        if (b0.y != nullptr) {
+            float u = b0.y[base + i];
+            for (int k = 1; k < b0.S; k++) u += b0.y[(size_t)k * slice + base + i];
+            v += b0.scale != nullptr ? ld_w(b0.scale, scale_dt, i) * u : u;
+        }
+        if (b1.y != nullptr) {
+            float u = b1.y[base + i];
+            for (int k = 1; k < b1.S; k++) u += b1.y[(size_t)k * slice + base + i];
+            v += b1.scale != nullptr ? ld_w(b1.scale, scale_dt, i) * u : u;
+        }
+        if (sums) x[base + i] = v;
+        row[i] = v;
+    }
+    if (o0.out == nullptr && o1.out == nullptr) return;
+    __syncthreads();
+    float mean = 0.f;
+    if (!rms) {
+        float s = 0.f;
+        for (int i = threadIdx.x; i < D; i += blockDim.x) s += row[i];
+        mean = gfb_block_sum(s, scratch) / (float)D;
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) { const float dv = row[i] - mean; ss += dv * dv; }
+    const float var = gfb_block_sum(ss, scratch) / (float)D;
+    if (o0.out != nullptr) {
+        const float rstd = 1.0f / sqrtf(var + o0.eps);
+        TO* o = (TO*)o0.out + (size_t)r * D;
+        for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = gfb_from_f32<TO>((row[i] - mean) * rstd * ld_w(o0.w, w_dt, i));
+    }
+    if (o1.out != nullptr) {
+        const float rstd = 1.0f / sqrtf(var + o1.eps);
+        TO* o = (TO*)o1.out + (size_t)r * D;
+        for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = gfb_from_f32<TO>((row[i] - mean) * rstd * ld_w(o1.w, w_dt, i));
+    }
+}
+
+// x float32 [T, D].  Branch b (y_b null: none): float32 [max(S_b,1)][T][D] with the per-column factor scale_b ([D] of
+// scale_dt, or null).  Output k (out_k null: none): [R, D] of out_dt = norm of the new x with weight w_k and eps_k.
+// rows (or null) gathers input rows and cannot be combined with a branch.
+GFB_API int gfb_layernorm_multi(float* x, const float* y0, int S0, const void* scale0, const float* y1, int S1,
+                                const void* scale1, int scale_dt, long slice, const void* w0, float eps0, void* out0,
+                                const void* w1, float eps1, void* out1, int w_dt, int out_dt, const int* rows, int R, int D,
+                                int rms, cudaStream_t stream) {
+    if (R <= 0 || D <= 0) return 0;
+    if ((y0 != nullptr || y1 != nullptr) && rows != nullptr) return gfb_fail("gfb_layernorm_multi: a branch sum cannot be combined with a row gather");
+    if (y0 == nullptr && y1 == nullptr && out0 == nullptr && out1 == nullptr) return 0;
+    if ((size_t)D * sizeof(float) > 200 * 1024) return gfb_fail("gfb_layernorm_multi: a row of %d elements does not fit shared memory", D);
+    LnBranch b0{y0, S0, scale0}, b1{y1, S1, scale1};
+    LnOut o0{w0, eps0, out0}, o1{w1, eps1, out1};
+    const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
+    const size_t smem = (size_t)D * sizeof(float);
+    cudaError_t e;
+#define GO(TO)                                                                                                         \
+    do {                                                                                                               \
+        static size_t allowed = 48 * 1024;                                                                             \
+        if (smem > allowed) {                                                                                          \
+            cudaFuncSetAttribute(layernorm_multi_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            allowed = 200 * 1024;                                                                                      \
+        }                                                                                                              \
+        e = gfb_launch(layernorm_multi_kernel<TO>, dim3(R), dim3(threads), smem, stream, x, b0, b1, scale_dt,          \
+                       (size_t)slice, o0, o1, w_dt, rows, D, rms);                                                     \
+    } while (0)
+    if ((out0 == nullptr && out1 == nullptr) || out_dt == GFB_F32) GO(float);
+    else if (out_dt == GFB_BF16) GO(__nv_bfloat16);
+    else return gfb_fail("gfb_layernorm_multi: unknown output type %d", out_dt);
+#undef GO
+    return gfb_check(e, "gfb_layernorm_multi");
 }

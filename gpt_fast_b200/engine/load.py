@@ -35,15 +35,15 @@ def load(source: Union[str, os.PathLike, dict], dtype="bfloat16", device="cuda",
         cfg["num_hidden_layers"] = n_layers
     arch = architecture_for(cfg)
     args = arch.parse(cfg)
-    spec = arch.build_spec(args)
-    plan = arch.weight_plan(args)
+    ckpt = None if random_weights else SafetensorsCheckpoint(folder)
+    extra = (None if ckpt is None else ckpt.shapes(),) if arch.shapes_from_checkpoint else ()
+    spec = arch.build_spec(args, *extra)
+    plan = arch.weight_plan(args, *extra)
     dt = compute_dtype(dtype)
     model = Transformer(spec, dt, device)
     if random_weights:
         dev = torch.device(device)
         ckpt = RandomCheckpoint(plan, seed, gen_device=dev if dev.type == "cuda" else "cpu")
-    else:
-        ckpt = SafetensorsCheckpoint(folder)
     params = load_parameters(plan, ckpt, model.param_specs(), dt, device, progress)
     model.load_params(params)
     model.args = args

@@ -16,8 +16,10 @@ from ..cache import Cache, CacheNeeds
 from ..config.spec import ModelSpec, PartSpec
 from ..ops.types import BatchMeta
 from ..parts.residual import Residual
-from ..parts import NORMS, POSITIONS, build_block, build_part
+from ..parts import EMBEDDINGS, NORMS, POSITIONS, build_block, build_part
 from ..weights.loader import ParamSpec
+
+EMBEDDING_CACHE_ENTRY = -1        # the cache entry of the embedding part's per-sequence state (layers count from 0)
 
 COMPUTE_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -55,6 +57,7 @@ class Transformer:
         self.blocks = [build_block(ls, spec.dim, self.dtype, position_for(ls.position)) for ls in spec.layers]
         self.positions = [obj for _, obj in positions]
         self.final_norm = build_part(NORMS, spec.final_norm, dtype=self.dtype)
+        self.embedding = None if spec.embedding is None else build_part(EMBEDDINGS, spec.embedding, dtype=self.dtype)
         self.embed_weight = None
         self.head_weight = None
 
@@ -64,6 +67,9 @@ class Transformer:
                  "head.weight": ParamSpec((self.vocab_size, self.dim))}
         for name, s in self.final_norm.param_specs().items():
             specs[f"final_norm.{name}"] = s
+        if self.embedding is not None:
+            for name, s in self.embedding.param_specs().items():
+                specs[f"embedding.{name}"] = s
         for i, b in enumerate(self.blocks):
             for pname, part in b.parts().items():
                 for name, s in part.param_specs().items():
@@ -87,6 +93,8 @@ class Transformer:
         if self.spec.tie_embeddings and self.head_weight.data_ptr() != self.embed_weight.data_ptr():
             raise ValueError("the spec ties the output to the embedding, but two tensors were given")
         self.final_norm.load(sub("final_norm."))
+        if self.embedding is not None:
+            self.embedding.load(sub("embedding."))
         for i, b in enumerate(self.blocks):
             for pname, part in b.parts().items():
                 part.load(sub(f"layers.{i}.{pname}."))
@@ -97,6 +105,9 @@ class Transformer:
         out = {"embed.weight": self.embed_weight, "head.weight": self.head_weight}
         for name, t in self.final_norm.export().items():
             out[f"final_norm.{name}"] = t
+        if self.embedding is not None:
+            for name, t in self.embedding.export().items():
+                out[f"embedding.{name}"] = t
         for i, b in enumerate(self.blocks):
             for pname, part in b.parts().items():
                 if not hasattr(part, "export"):
@@ -109,6 +120,8 @@ class Transformer:
         """Whether a step of this model may be captured in a CUDA graph: every part launches kernels only.  A part
         that reads device values on the host says so with `graph_safe = False`."""
         parts = [self.final_norm] + [p for b in self.blocks for p in b.parts().values()] + list(self.positions)
+        if self.embedding is not None:
+            parts.append(self.embedding)
         return all(getattr(p, "graph_safe", True) for p in parts + list(self.blocks))
 
     def weight_bytes(self, with_embedding=False) -> int:
@@ -136,6 +149,8 @@ class Transformer:
     # ---- cache ---------------------------------------------------------------------
     def cache_needs(self) -> Dict[int, CacheNeeds]:
         needs = {}
+        if self.embedding is not None:
+            needs[EMBEDDING_CACHE_ENTRY] = self.embedding.cache_needs()
         for e in self.spec.schedule:
             if e.owns_cache:
                 needs[e.cache] = self.blocks[e.layer].cache_needs()
@@ -176,7 +191,11 @@ class Transformer:
         and values to the cache; the caller advances the lengths afterwards."""
         T = batch.n_tokens
         x = torch.empty(T, self.dim, dtype=torch.float32, device=self.device)
-        ops.embed(tokens, self.embed_weight, x, batch.status, 1.0 if self.spec.embed_scale is None else float(self.spec.embed_scale))
+        scale = 1.0 if self.spec.embed_scale is None else float(self.spec.embed_scale)
+        if self.embedding is None:
+            ops.embed(tokens, self.embed_weight, x, batch.status, scale)
+        else:
+            self.embedding.forward(tokens, self.embed_weight, x, batch, cache.view(EMBEDDING_CACHE_ENTRY), scale)
         x = Residual(x)
         for e in self.spec.schedule:
             self.blocks[e.layer].forward(x, batch, cache.view(e.cache), append=e.owns_cache)

@@ -92,6 +92,14 @@ def embed(tokens, table, out, status, scale: float = 1.0):
     return kernels().embed(tokens, table, out, status, scale)
 
 
+def embed_hashed(tokens, table, extra, out, batch: BatchMeta, prev, buckets: int, mul_prev: int, mul_cur: int, scale: float = 1.0):
+    """out[t] = table[tokens[t]] * scale + extra[(previous token * mul_prev + tokens[t] * mul_cur) mod buckets], with
+    extra's row `buckets` for a sequence's first token.  extra [buckets + 1, D]; prev int32 [n_slots] is per-sequence
+    state: the token before a step's first one is read from it, and every sequence's last token of the step is
+    written to it afterwards."""
+    return kernels().embed_hashed(tokens, table, extra, out, batch, prev, buckets, mul_prev, mul_cur, scale)
+
+
 def softcap(x, cap: float):
     """x (float32, in place) = cap * tanh(x / cap)."""
     return kernels().softcap(x, cap)
@@ -106,13 +114,81 @@ def rmsnorm(x, weight, eps: float, out, rows=None, pending=None):
 
 
 def layernorm(x, weight, bias, eps: float, out, rows=None, branch=None, rms: bool = False):
-    """Layer norm with weight and bias, (v - mean) / sqrt(mean((v - mean)^2) + eps) * weight + bias, statistics in
-    32-bit.  x float32 [T, D]; out [R, D] in the compute type, or None; rows int32 [R] or None.
+    """Layer norm with weight and bias (bias None: none), (v - mean) / sqrt(mean((v - mean)^2) + eps) * weight + bias,
+    statistics in 32-bit.  x float32 [T, D]; out [R, D] in the compute type, or None; rows int32 [R] or None.
     branch = (y, weight, bias, eps, mult), only without rows: the kernel first completes
     x += mult * norm(y) with that norm's parameters (written back), y being a float32 [T, D] tensor or partial sums
     [S, T, D] of it, and then norms the new x into `out` (if given).  rms=True: the root-mean-square form, no mean
     and no bias, for both norms."""
     return kernels().layernorm(x, weight, bias, eps, out, rows, branch, rms)
+
+
+def layernorm_multi(x, branches=(), outs=(), rows=None, rms: bool = False):
+    """One row, one mean and variance, several norms.  x float32 [T, D].  branches: up to two (y, scale): first
+    x += scale * y (written back), y a float32 [T, D] tensor or partial sums [S, T, D] added in ascending order,
+    scale a per-column factor [D] or None.  outs: up to two (weight, eps, out): out [R, D] = (x - mean) / sqrt(var +
+    eps) * weight in the compute type.  rows int32 [R] gathers input rows (not together with branches).  rms=True:
+    the root-mean-square form (no mean)."""
+    return kernels().layernorm_multi(x, branches, outs, rows, rms)
+
+
+def latent_prepare(src, q_off: int, kv_off: int, q_out, kv: PagedKV, batch: BatchMeta, n_head: int, head_dim: int,
+                   rot_dim: int, rank: int, norm_weight, eps: float, table, pairing: str = "interleaved", append: bool = True):
+    """Latent attention's per-token work.  src [T, W] holds, at column q_off, n_head heads of (head_dim unrotated +
+    rot_dim rotated) query numbers and, at kv_off, rank + rot_dim numbers of the down projection.  The first rank of
+    those, divided by their root mean square (eps inside the root) and times norm_weight, are the latent; the last
+    rot_dim are rotated by the token's position (table float32 [P, rot_dim/2, 2]).  Both go to the token's place in
+    the cache as ONE key row of rank + rot_dim numbers (one key head; the value pool is not used).  Every head's
+    rotated query part is turned too and written to q_out[t, h, rank:], q_out being [T, n_head, rank + rot_dim]."""
+    return kernels().latent_prepare(src, q_off, kv_off, q_out, kv, batch, n_head, head_dim, rot_dim, rank, norm_weight, eps,
+                                    table, pairing, append)
+
+
+def headwise_linear(a, w, out, n_head: int, k: int, n: int, a_off: int = 0, a_stride: Optional[int] = None, out_off: int = 0,
+                    out_stride: Optional[int] = None, layout: str = "kn", gate=None, gate_off: int = 0):
+    """A product with a weight per head: out[t, h, :] = W_h applied to a[t, h, :].  a [T, Wa]: head h's k inputs start
+    at column a_off + h * a_stride; out [T, Wo]: its n outputs at out_off + h * out_stride; w [n_head, k, n]
+    (layout 'kn': out = a W_h) or [n_head, n, k] ('nk': out = W_h a).  gate [T, Wg] (or None): the result is
+    multiplied by sigmoid(gate[t, gate_off + h * n + j])."""
+    return kernels().headwise_linear(a, w, out, n_head, k, n, a_off, a_stride, out_off, out_stride, layout, gate, gate_off)
+
+
+def short_conv(src, col_off: int, channels: int, weight, bias, state, state_off: int, out, batch: BatchMeta, act: bool = True):
+    """Causal convolution over time per channel, then SiLU (act).  src [T, W]: the channels start at column col_off;
+    weight [channels, taps], whose last column meets the current token; bias [channels] or None; out float32 [T,
+    channels].  state float32 [n_slots, S]: from column state_off, the (taps - 1) * channels latest inputs of each
+    sequence, oldest first (zeros at a sequence's start); read for the tokens at a step's start and advanced."""
+    return kernels().short_conv(src, col_off, channels, weight, bias, state, state_off, out, batch, act)
+
+
+def ssd_scan(x, b_off: int, c_off: int, dt_src, dt_off: int, dt_bias, a_log, skip, state, state_off: int, out,
+             batch: BatchMeta, n_head: int, head_dim: int, n_state: int, n_groups: int):
+    """Selective state space, token after token: per head h (group g = h // (n_head / n_groups))
+    dt = softplus(dt_raw + dt_bias[h]);  S <- exp(-exp(a_log[h]) dt) S + dt B_g x_h^T;  y = S^T C_g + skip[h] x_h.
+    x float32 [T, W]: heads of head_dim at column 0, B groups of n_state at b_off, C at c_off; dt_raw = dt_src[:, dt_off
+    + h]; state float32 [n_slots, S] holds [n_head, n_state, head_dim] per sequence from column state_off; out float32
+    [T, n_head, head_dim]."""
+    return kernels().ssd_scan(x, b_off, c_off, dt_src, dt_off, dt_bias, a_log, skip, state, state_off, out, batch, n_head,
+                              head_dim, n_state, n_groups)
+
+
+def delta_rule(qkv, offsets, beta_src, beta_off: int, a_src, a_off: int, dt_bias, a_log, state, state_off: int, out,
+               batch: BatchMeta, n_head: int, n_qk: int, head_dim: int, v_head_dim: int, q_scale: float, unit_eps: float = 1e-6):
+    """Gated delta rule, token after token: per head h (query/key head j = h // (n_head / n_qk)), with q and k divided
+    by sqrt(sum of squares + unit_eps) (q also times q_scale), beta = sigmoid(beta_src[:, beta_off + h]) and
+    g = exp(-exp(a_log[h]) softplus(a_src[:, a_off + h * head_dim + i] + dt_bias[h * head_dim + i])):
+    S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+    qkv float32 [T, W] with q, k, v at the column offsets `offsets`; a_src float32; state float32 [n_slots, S] holds
+    [n_head, head_dim, v_head_dim] per sequence from column state_off; out float32 [T, n_head, v_head_dim]."""
+    return kernels().delta_rule(qkv, offsets, beta_src, beta_off, a_src, a_off, dt_bias, a_log, state, state_off, out, batch,
+                                n_head, n_qk, head_dim, v_head_dim, q_scale, unit_eps)
+
+
+def gated_norm(y, gate, gate_off: int, weight, out, group: int, eps: float, act: str = "silu", gate_first: bool = False):
+    """Root-mean-square norm over groups of `group` columns with a gate: v = y (times act(gate) first if gate_first),
+    out = v / sqrt(mean(v^2) + eps) * weight[column mod len(weight)] (times act(gate) here otherwise).  y float32
+    [T, C]; gate [T, Wg] from column gate_off; act 'silu' or 'sigmoid'; out [T, C] in the compute type."""
+    return kernels().gated_norm(y, gate, gate_off, weight, out, group, eps, act, gate_first)
 
 
 def qkv_prepare(src, partials, offsets, q_out, kv: PagedKV, batch: BatchMeta, n_head: int, n_kv: int, head_dim: int,
@@ -144,7 +220,7 @@ def retention_gate(o, src, gate_offset: int, out, n_head: int, v_head_dim: int, 
 
 
 def activation(x, kind: str, out=None):
-    """out (default: in place) = f(x) with f 'gelu' (exact, erf), 'gelu_tanh' or 'silu'."""
+    """out (default: in place) = f(x) with f 'gelu' (exact, erf), 'gelu_tanh', 'silu' or 'relu2' (max(x, 0)^2)."""
     return kernels().activation(x, kind, out)
 
 
@@ -152,7 +228,7 @@ def linear(a, w, out, mode: str = "store", defer: bool = False):
     """a [M, K] times w [N, K] transposed.  mode 'store': out [M, N] = product;
     'add': out float32 [M, N] += product (the residual sum, in 32-bit);
     'swiglu': w's rows alternate gate, up and out [M, N/2] = silu(gate) * up;
-    'gelu' (exact, erf), 'gelu_tanh', 'silu': out [M, N] = f(product).
+    'gelu' (exact, erf), 'gelu_tanh', 'silu', 'relu2': out [M, N] = f(product).
 
     defer=True (modes 'store' and 'add'): if the kernel splits the sum over K it
     may return the partial sums (float32 [S, M, N]) INSTEAD of finishing `out`;
@@ -167,9 +243,11 @@ def add_partials(x, pending):
     return kernels().add_partials(x, pending)
 
 
-def rope_table(inv_freq, table):
-    """table[p, i] = (cos, sin)(p * inv_freq[i]) in 32-bit.  table float32 [P, d/2, 2]."""
-    return kernels().rope_table(inv_freq, table)
+def rope_table(inv_freq, table, amplitude: float = 1.0):
+    """table[p, i] = amplitude * (cos, sin)(p * inv_freq[i]) in 32-bit.  table float32 [P, d/2, 2]."""
+    if amplitude == 1.0:
+        return kernels().rope_table(inv_freq, table)
+    return kernels().rope_table(inv_freq, table, amplitude)
 
 
 def rope_append(qkv, q_out, kv: PagedKV, batch: BatchMeta, table, n_head: int, n_kv: int, head_dim: int,
@@ -182,11 +260,16 @@ def rope_append(qkv, q_out, kv: PagedKV, batch: BatchMeta, table, n_head: int, n
 
 
 def attention(q, kv: PagedKV, batch: BatchMeta, out, n_head: int, n_kv: int, head_dim: int, scale: float,
-              window: Optional[int] = None, chunk: Optional[int] = None, sink=None, v_head_dim: Optional[int] = None):
+              window: Optional[int] = None, chunk: Optional[int] = None, sink=None, v_head_dim: Optional[int] = None,
+              values_in_keys: bool = False):
     """Causal grouped-query attention of q [T, H, d] over the cache (which
     already holds this step's keys and values); out [T, H*dv].  chunk: a query sees only the keys of its own block
     of `chunk` positions (counted from the sequence's first position).  sink (float32 [H]): exp(sink_h) joins the
-    softmax denominator of head h, with no value.  v_head_dim: the values' head size if it differs from d."""
+    softmax denominator of head h, with no value.  v_head_dim: the values' head size if it differs from d.
+    values_in_keys: a key's first v_head_dim numbers are also its value (the value pool is not read)."""
+    if values_in_keys:
+        return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk, sink, v_head_dim or head_dim,
+                                   values_in_keys=True)
     if chunk is None and sink is None and v_head_dim in (None, head_dim):
         return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window)
     return kernels().attention(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk, sink, v_head_dim or head_dim)

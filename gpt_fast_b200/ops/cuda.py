@@ -10,8 +10,9 @@ from ..csrc import build
 from .types import BatchMeta, PagedKV
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
-_EPI = {"store": 0, "add": 1, "swiglu": 2, "gelu": 4, "gelu_tanh": 5, "silu": 6}
-_UNARY = ("gelu", "gelu_tanh", "silu")
+_EPI = {"store": 0, "add": 1, "swiglu": 2, "gelu": 4, "gelu_tanh": 5, "silu": 6, "relu2": 7}
+_UNARY = ("gelu", "gelu_tanh", "silu", "relu2")
+_TC_UNARY = ("gelu", "relu2")             # the unary epilogues the tensor-core product has (they store bfloat16)
 _PAIRING = {"interleaved": 0, "half": 1}
 
 
@@ -116,6 +117,18 @@ class CudaKernels:
         self._call("core", "gfb_embed", _ptr(tokens), _ptr(table), c_int(_dt(table)), _ptr(out),
                    c_int(T), c_int(D), c_int(V), c_float(scale), _ptr(status), _stream())
 
+    def embed_hashed(self, tokens, table, extra, out, batch, prev, buckets, mul_prev, mul_cur, scale=1.0):
+        T = tokens.shape[0]
+        V, D = table.shape
+        _need(tokens, torch.int32, (batch.n_tokens,), "tokens")
+        _need(table, name="embedding table")
+        _need(extra, table.dtype, (buckets + 1, D), "hashed embedding table")
+        _need(out, torch.float32, (T, D), "embedding output")
+        _need(prev, torch.int32, name="previous tokens")
+        self._call("embedding", "gfb_embed_hashed", _ptr(tokens), _ptr(table), _ptr(extra), c_int(_dt(table)), _ptr(out),
+                   *self._batch_args(batch), _ptr(prev), c_int(D), c_int(V), c_int(buckets), c_int(mul_prev), c_int(mul_cur),
+                   c_float(scale), _ptr(batch.status), _stream())
+
     def softcap(self, x, cap):
         _need(x, torch.float32, name="logits")
         self._call("core", "gfb_softcap", _ptr(x), c_long(x.numel()), c_float(cap), _stream())
@@ -145,11 +158,11 @@ class CudaKernels:
         _need(pending, torch.float32, (pending.shape[0],) + tuple(x.shape), "pending partial sums")
         self._call("core", "gfb_add_partials", _ptr(x), _ptr(pending), c_int(pending.shape[0]), c_long(x.numel()), _stream())
 
-    def rope_table(self, inv_freq, table):
+    def rope_table(self, inv_freq, table, amplitude=1.0):
         P, half, two = table.shape
         _need(inv_freq, torch.float32, (half,), "inv_freq")
         _need(table, torch.float32, name="rotary table")
-        self._call("core", "gfb_rope_table", _ptr(inv_freq), _ptr(table), c_int(P), c_int(half), _stream())
+        self._call("core", "gfb_rope_table", _ptr(inv_freq), _ptr(table), c_int(P), c_int(half), c_float(amplitude), _stream())
 
     def _batch_args(self, b: BatchMeta):
         return (_ptr(b.cu_seqlens), _ptr(b.tok_seq), _ptr(b.slots), _ptr(b.lengths), c_int(b.n_seqs), c_int(b.n_tokens))
@@ -194,7 +207,7 @@ class CudaKernels:
         if out is not None:
             R = out.shape[0]
             _need(weight, shape=(D,), name="norm weight")
-            if not rms:
+            if not rms and bias is not None:
                 _need(bias, weight.dtype, (D,), "norm bias")
             _need(out, shape=(R, D), name="norm output")
             if rows is not None:
@@ -210,7 +223,7 @@ class CudaKernels:
             if rows is not None:
                 _fail("a branch sum cannot be combined with a row gather")
             _need(pw, shape=(D,), name="branch norm weight")
-            if not rms:
+            if not rms and pb is not None:
                 _need(pb, pw.dtype, (D,), "branch norm bias")
             if y.dim() == 3:
                 S = y.shape[0]
@@ -224,6 +237,166 @@ class CudaKernels:
                    _ptr(bias if out is not None else None), c_int(_dt(weight) if out is not None else 0), c_float(eps),
                    _ptr(out), c_int(_dt(out) if out is not None else 0), _ptr(rows), c_int(R), c_int(D), c_int(1 if rms else 0),
                    _stream())
+
+    def layernorm_multi(self, x, branches=(), outs=(), rows=None, rms=False):
+        T, D = x.shape
+        _need(x, torch.float32, name="norm input")
+        if len(branches) > 2 or len(outs) > 2:
+            _fail("at most two branches and two outputs")
+        if branches and rows is not None:
+            _fail("a branch sum cannot be combined with a row gather")
+        b_args, scale_dt = [], 0
+        for y, scale in list(branches) + [(None, None)] * (2 - len(branches)):
+            S = 0
+            if y is not None:
+                if y.dim() == 3:
+                    S = y.shape[0]
+                    _need(y, torch.float32, (S, T, D), "partial sums of a branch")
+                else:
+                    _need(y, torch.float32, (T, D), "branch")
+                if scale is not None:
+                    _need(scale, shape=(D,), name="branch factor")
+                    scale_dt = _dt(scale)
+            b_args += [_ptr(y), c_int(S), _ptr(scale)]
+        scales = [s for _, s in branches if s is not None]
+        if len(scales) == 2 and scales[0].dtype != scales[1].dtype:
+            _fail("the branch factors must have one type")
+        o_args, w_dt, out_dt, R = [], 0, 0, T
+        for w, eps, out in list(outs) + [(None, 0.0, None)] * (2 - len(outs)):
+            if out is not None:
+                R = out.shape[0]
+                _need(w, shape=(D,), name="norm weight")
+                _need(out, shape=(R, D), name="norm output")
+                w_dt, out_dt = _dt(w), _dt(out)
+            o_args += [_ptr(w), c_float(eps), _ptr(out)]
+        if len(outs) == 2 and (outs[0][0].dtype != outs[1][0].dtype or outs[0][2].dtype != outs[1][2].dtype
+                               or outs[0][2].shape != outs[1][2].shape):
+            _fail("the two outputs must agree in shape and types")
+        if rows is not None:
+            _need(rows, torch.int32, (R,), "rows")
+        elif outs and R != T:
+            _fail(f"norm output has {R} rows, input {T}")
+        if not branches and not outs:
+            return
+        self._call("layernorm", "gfb_layernorm_multi", _ptr(x), *b_args[:3], *b_args[3:], c_int(scale_dt), c_long(T * D),
+                   *o_args[:3], *o_args[3:], c_int(w_dt), c_int(out_dt), _ptr(rows), c_int(R), c_int(D), c_int(1 if rms else 0),
+                   _stream())
+
+    def latent_prepare(self, src, q_off, kv_off, q_out, kv, batch, n_head, head_dim, rot_dim, rank, norm_weight, eps, table,
+                       pairing="interleaved", append=True):
+        T = batch.n_tokens
+        W = src.shape[1]
+        _need(src, q_out.dtype, (T, W), "projection")
+        if max(q_off + n_head * (head_dim + rot_dim), kv_off + rank + rot_dim) > W:
+            _fail(f"queries at {q_off} and the down projection at {kv_off} do not fit rows of {W}")
+        _need(q_out, shape=(T, n_head, rank + rot_dim), name="q_out")
+        _need(norm_weight, shape=(rank,), name="latent norm weight")
+        _need(table, torch.float32, name="rotary table")
+        if table.shape[1] * 2 != rot_dim:
+            _fail(f"the rotary table serves {table.shape[1] * 2} dimensions, the mixer rotates {rot_dim}")
+        if append:
+            _need(kv.k_pool, q_out.dtype, name="key pool")
+            if tuple(kv.k_pool.shape[1:]) != (1, kv.page_size, rank + rot_dim):
+                _fail(f"cache pages are {tuple(kv.k_pool.shape[1:])}, the layer needs {(1, kv.page_size, rank + rot_dim)}")
+        self._call("latent", "gfb_latent_prepare", _ptr(src), c_int(_dt(src)), c_int(W), c_int(q_off), c_int(kv_off), _ptr(q_out),
+                   _ptr(kv.k_pool), _ptr(kv.page_table), c_int(kv.page_table.shape[1]), c_int(kv.page_size), c_int(kv.k_pool.shape[0]),
+                   *self._batch_args(batch), _ptr(table), c_int(table.shape[0]), _ptr(norm_weight), c_int(_dt(norm_weight)),
+                   c_float(eps), c_int(n_head), c_int(head_dim), c_int(rot_dim), c_int(rank), c_int(_PAIRING[pairing]),
+                   c_int(1 if append else 0), _ptr(batch.status), _stream())
+
+    def headwise_linear(self, a, w, out, n_head, k, n, a_off=0, a_stride=None, out_off=0, out_stride=None, layout="kn",
+                        gate=None, gate_off=0):
+        T = a.shape[0]
+        a_stride = k if a_stride is None else a_stride
+        out_stride = n if out_stride is None else out_stride
+        _need(a, name="head-wise input")
+        _need(out, a.dtype, name="head-wise output")
+        if a.dim() != 2 or out.dim() != 2 or out.shape[0] != T:
+            _fail("head-wise product: input and output are [tokens, columns]")
+        _need(w, a.dtype, (n_head, k, n) if layout == "kn" else (n_head, n, k), "head-wise weight")
+        if a_off + (n_head - 1) * a_stride + k > a.shape[1] or out_off + (n_head - 1) * out_stride + n > out.shape[1]:
+            _fail("head-wise product: the heads do not fit the rows")
+        if gate is not None:
+            _need(gate, a.dtype, name="gate")
+            if gate.shape[0] != T or gate_off + n_head * n > gate.shape[1]:
+                _fail("head-wise product: the gate does not fit")
+        self._call("latent", "gfb_headwise_linear", _ptr(a), c_int(_dt(a)), c_int(a.shape[1]), c_int(a_off), c_int(a_stride), _ptr(w),
+                   c_int(1 if layout == "kn" else 0), _ptr(out), c_int(out.shape[1]), c_int(out_off), c_int(out_stride), _ptr(gate),
+                   c_int(gate.shape[1] if gate is not None else 0), c_int(gate_off), c_int(T), c_int(n_head), c_int(k), c_int(n),
+                   _stream())
+
+    @staticmethod
+    def _state_args(state, state_off, need):
+        _need(state, torch.float32, name="per-sequence state")
+        if state.dim() != 2 or state_off < 0 or state_off + need > state.shape[1]:
+            _fail(f"{need} numbers of state at column {state_off} do not fit rows of {tuple(state.shape)}")
+        return c_void_p(state.data_ptr() + 4 * state_off), c_long(state.shape[1])
+
+    def short_conv(self, src, col_off, channels, weight, bias, state, state_off, out, batch, act=True):
+        T = batch.n_tokens
+        taps = weight.shape[1]
+        _need(src, name="convolution input")
+        if src.shape[0] != T or col_off + channels > src.shape[1]:
+            _fail(f"{channels} channels at column {col_off} do not fit {tuple(src.shape)}")
+        _need(weight, shape=(channels, taps), name="convolution weight")
+        if bias is not None:
+            _need(bias, weight.dtype, (channels,), "convolution bias")
+        _need(out, torch.float32, (T, channels), "convolution output")
+        sp, sld = self._state_args(state, state_off, (taps - 1) * channels)
+        self._call("recurrent", "gfb_short_conv", _ptr(src), c_int(_dt(src)), c_int(src.shape[1]), c_int(col_off), c_int(channels),
+                   _ptr(weight), _ptr(bias), c_int(_dt(weight)), c_int(taps), sp, sld, _ptr(out), *self._batch_args(batch),
+                   c_int(1 if act else 0), _stream())
+
+    def ssd_scan(self, x, b_off, c_off, dt_src, dt_off, dt_bias, a_log, skip, state, state_off, out, batch, n_head, head_dim,
+                 n_state, n_groups):
+        T = batch.n_tokens
+        _need(x, torch.float32, name="scan input")
+        if x.shape[0] != T or max(n_head * head_dim, b_off + n_groups * n_state, c_off + n_groups * n_state) > x.shape[1]:
+            _fail(f"heads, B and C do not fit rows of {tuple(x.shape)}")
+        _need(dt_src, name="step sizes")
+        if dt_src.shape[0] != T or dt_off + n_head > dt_src.shape[1]:
+            _fail("the step sizes do not fit their rows")
+        for v, name in ((dt_bias, "dt_bias"), (a_log, "A_log")) + (((skip, "D"),) if skip is not None else ()):
+            _need(v, dt_bias.dtype, (n_head,), name)
+        _need(out, torch.float32, (T, n_head, head_dim), "scan output")
+        sp, sld = self._state_args(state, state_off, n_head * n_state * head_dim)
+        self._call("recurrent", "gfb_ssd_scan", _ptr(x), c_int(x.shape[1]), c_int(b_off), c_int(c_off), _ptr(dt_src), c_int(_dt(dt_src)),
+                   c_int(dt_src.shape[1]), c_int(dt_off), _ptr(dt_bias), _ptr(a_log), _ptr(skip), c_int(_dt(dt_bias)), sp, sld,
+                   _ptr(out), *self._batch_args(batch), c_int(n_head), c_int(head_dim), c_int(n_state), c_int(n_groups), _stream())
+
+    def delta_rule(self, qkv, offsets, beta_src, beta_off, a_src, a_off, dt_bias, a_log, state, state_off, out, batch, n_head,
+                   n_qk, head_dim, v_head_dim, q_scale, unit_eps=1e-6):
+        T = batch.n_tokens
+        q_off, k_off, v_off = offsets
+        _need(qkv, torch.float32, name="q, k, v")
+        if qkv.shape[0] != T or max(q_off + n_qk * head_dim, k_off + n_qk * head_dim, v_off + n_head * v_head_dim) > qkv.shape[1]:
+            _fail(f"q, k and v at {offsets} do not fit rows of {tuple(qkv.shape)}")
+        _need(beta_src, name="beta")
+        _need(a_src, torch.float32, name="decay input")
+        if beta_src.shape[0] != T or beta_off + n_head > beta_src.shape[1] or a_src.shape[0] != T or a_off + n_head * head_dim > a_src.shape[1]:
+            _fail("beta or the decay input do not fit their rows")
+        _need(dt_bias, shape=(n_head * head_dim,), name="dt_bias")
+        _need(a_log, dt_bias.dtype, (n_head,), "A_log")
+        _need(out, torch.float32, (T, n_head, v_head_dim), "delta-rule output")
+        sp, sld = self._state_args(state, state_off, n_head * head_dim * v_head_dim)
+        self._call("recurrent", "gfb_delta_rule", _ptr(qkv), c_int(qkv.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off),
+                   _ptr(beta_src), c_int(_dt(beta_src)), c_int(beta_src.shape[1]), c_int(beta_off), _ptr(a_src), c_int(a_src.shape[1]),
+                   c_int(a_off), _ptr(dt_bias), _ptr(a_log), c_int(_dt(dt_bias)), sp, sld, _ptr(out), *self._batch_args(batch),
+                   c_int(n_head), c_int(n_qk), c_int(head_dim), c_int(v_head_dim), c_float(q_scale), c_float(unit_eps), _stream())
+
+    def gated_norm(self, y, gate, gate_off, weight, out, group, eps, act="silu", gate_first=False):
+        T, C = y.shape
+        _need(y, torch.float32, name="norm input")
+        _need(gate, name="gate")
+        _need(out, shape=(T, C), name="gated output")
+        _need(weight, name="norm weight")
+        if C % group or gate.shape[0] != T or gate_off + C > gate.shape[1] or (C % weight.shape[0] and weight.shape[0] % group):
+            _fail(f"groups of {group}, a gate of {tuple(gate.shape)} at {gate_off} or a weight of {tuple(weight.shape)} do not fit {C} columns")
+        if act not in ("silu", "sigmoid"):
+            _fail(f"unknown gate activation '{act}'")
+        self._call("recurrent", "gfb_gated_norm", _ptr(y), _ptr(gate), c_int(_dt(gate)), c_int(gate.shape[1]), c_int(gate_off),
+                   _ptr(weight), c_int(_dt(weight)), c_int(weight.shape[0]), _ptr(out), c_int(_dt(out)), c_int(T), c_int(C // group),
+                   c_int(group), c_float(eps), c_int(1 if act == "sigmoid" else 0), c_int(1 if gate_first else 0), _stream())
 
     def qkv_prepare(self, src, partials, offsets, q_out, kv, batch, n_head, n_kv, head_dim, v_head_dim, table=None, rot_dims=0,
                     pairing="half", q_norm=None, k_norm=None, norm_eps=0.0, k_scale=1.0, append=True):
@@ -322,8 +495,8 @@ class CudaKernels:
             _fail(f"product of {a.dtype} cannot be stored as {out.dtype}")
         self._label = f"linear {N}x{K} {mode}"
         if a.dtype == torch.bfloat16 and self._tc_fits(M, N, K, mode):
-            if mode in _UNARY and not (mode == "gelu" and out.dtype == torch.bfloat16):
-                # only the exact GELU has an epilogue of its own in the tensor-core kernel
+            if mode in _UNARY and not (mode in _TC_UNARY and out.dtype == torch.bfloat16):
+                # the other activations have no epilogue of their own in the tensor-core kernel
                 self._linear_tc(a, w, out, "store")
                 return self.activation(out, mode)
             return self._linear_tc(a, w, out, mode, defer=defer and mode in ("store", "add"))
@@ -394,7 +567,8 @@ class CudaKernels:
         return None
 
     # -- attention ---------------------------------------------------------------------
-    def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None):
+    def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None,
+                  values_in_keys=False):
         T = batch.n_tokens
         dv = v_head_dim or head_dim
         _need(q, shape=(T, n_head, head_dim), name="q")
@@ -403,13 +577,14 @@ class CudaKernels:
         if sink is not None:
             _need(sink, torch.float32, (n_head,), "sink")
         plain = chunk is None and sink is None
-        if (dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
+        if (not values_in_keys and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
                 and (head_dim in (64, 128) or (plain and head_dim % 8 == 0 and head_dim <= 256))):
             # the tensor-core kernels; a block mask or a sink only at the head sizes they are built for
             return self._attention_bf16(q, kv, batch, out, n_head, n_kv, head_dim, scale, window, chunk=chunk, sink=sink)
         self._call("attention_generic", "gfb_attention_generic", _ptr(q), _ptr(out), c_int(_dt(q)),
                    *self._kv_args(kv), *self._batch_args(batch), c_int(n_head), c_int(n_kv), c_int(head_dim), c_int(dv),
-                   c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink), _ptr(batch.status), _stream())
+                   c_float(scale), c_int(window or 0), c_int(chunk or 0), _ptr(sink), c_int(1 if values_in_keys else 0),
+                   _ptr(batch.status), _stream())
 
     def decode_slices(self, max_kv_len, page_size, blocks) -> int:
         return decode_slices(max_kv_len, page_size, blocks, self.sm_count)

@@ -2,13 +2,14 @@
 
 A part is a small class that owns its parameters and launches kernels through
 `ops`; it takes its sizes and constants as constructor arguments and never
-sees the model's configuration.  Five kinds, one registry each:
+sees the model's configuration.  Six kinds, one registry each:
 
     NORMS          forward(x32 [T,D], out [R,D], rows=None)
     POSITIONS      prepare(max_positions, device); what a mixer needs to place tokens
     MIXERS         cache_needs(); forward(h, batch, view, residual, append)
     FEED_FORWARDS  forward(h, residual)
     BLOCKS         roles; cache_needs(); forward(x32, batch, view, append): the arrangement of the above
+    EMBEDDINGS     cache_needs(); forward(tokens, table, out, batch, view, scale): the token embedding plus something
 
 Every part also has `param_specs()` (name -> weights.loader.ParamSpec) and
 `load(tensors)`.  Mixers and feed-forwards ADD their result into `residual`, the
@@ -27,6 +28,7 @@ POSITIONS: Dict[str, Callable] = {}
 MIXERS: Dict[str, Callable] = {}
 FEED_FORWARDS: Dict[str, Callable] = {}
 BLOCKS: Dict[str, Callable] = {}
+EMBEDDINGS: Dict[str, Callable] = {}
 
 # kind of part -> registry; a block arrangement names a kind for each of its roles
 REGISTRIES: Dict[str, Dict[str, Callable]] = {"norm": NORMS, "position": POSITIONS, "mixer": MIXERS,
@@ -50,6 +52,7 @@ register_position = _registrar(POSITIONS, "position encoding")
 register_mixer = _registrar(MIXERS, "mixer")
 register_feed_forward = _registrar(FEED_FORWARDS, "feed-forward")
 register_block = _registrar(BLOCKS, "block")
+register_embedding = _registrar(EMBEDDINGS, "embedding")
 
 
 def build_block(layer, dim: int, dtype, position):
@@ -84,3 +87,4 @@ def build_part(table: Dict[str, Callable], spec: PartSpec, **extra: Any):
 
 
 from . import norm, rope, attention, retention, feed_forward, block  # noqa: E402,F401  (register the built-in parts)
+from . import embedding, latent_attention, state_space, delta_rule  # noqa: E402,F401

@@ -1,7 +1,8 @@
 """Arrangements of a layer's parts.  'prenorm' is gpt-fast's TransformerBlock
 (model.py:153-164): x += mixer(norm(x)); x += feed_forward(norm(x)), with the
 residual stream x kept in 32-bit.  'sandwich' norms a sublayer's output as well
-and scales it before the sum; its feed-forward is optional.
+and scales it before the sum; its feed-forward is optional.  'parallel' runs mixer and
+feed-forward side by side on two norms of the same x.
 
 An arrangement declares `roles`: the names of the parts it is made of, each with
 the kind of part that fills it ('mixer', 'feed_forward', 'norm': the registries of
@@ -9,6 +10,8 @@ the kind of part that fills it ('mixer', 'feed_forward', 'norm': the registries 
 and hands them over as a dict; mixers also receive the layer's position encoding."""
 import torch
 
+from .. import ops
+from ..weights.loader import ParamSpec
 from . import register_block
 from .residual import Branch, as_residual
 
@@ -82,3 +85,70 @@ class SandwichBlock:
             y = Branch(T, self.dim, dev)
             self.feed_forward.forward(h, residual=y)
             x.add_normed(y, self.ffn_post_norm, self.mult)
+
+
+class LayerScale:
+    """A learned factor per column on a sublayer's output."""
+
+    def __init__(self, dim: int):
+        self.dim = dim
+        self.weight = None
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.dim,), "vector")}
+
+    def load(self, tensors):
+        self.weight = tensors["weight"]
+
+    def export(self):
+        return {"weight": self.weight}
+
+
+@register_block("parallel")
+class ParallelBlock:
+    """Mixer and feed-forward read two norms of the SAME x and their results are added together:
+
+        x += s1 * mixer(norm1(x)) + s2 * feed_forward(norm2(x))
+
+    s1, s2: learned per-column factors (`layer_scale`; without it they are 1).  The feed-forward with its norm is
+    optional.  The two norms share mean and variance and differ in their weights, so one kernel writes both normed
+    rows; the two scaled sums are left to the stream and done by the next layer's norm kernel on its way
+    (`Residual.add_scaled`).  The norms are layer norms without bias."""
+    roles = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "ffn_norm": "norm"}
+    optional_roles = ("feed_forward", "ffn_norm")
+
+    def __init__(self, parts: dict, dim: int, dtype: torch.dtype, layer_scale: bool = False):
+        if ("feed_forward" in parts) != ("ffn_norm" in parts):
+            raise ValueError("a parallel block has a feed-forward together with its norm, or neither")
+        self._parts = dict(parts)
+        self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
+        self.feed_forward, self.ffn_norm = parts.get("feed_forward"), parts.get("ffn_norm")
+        self.dim, self.dtype = dim, dtype
+        self.mixer_scale = self.ffn_scale = None
+        if layer_scale:
+            self.mixer_scale = self._parts["mixer_scale"] = LayerScale(dim)
+            if self.feed_forward is not None:
+                self.ffn_scale = self._parts["ffn_scale"] = LayerScale(dim)
+
+    def parts(self):
+        return dict(self._parts)
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def forward(self, x, batch, view, append: bool = True):
+        x = as_residual(x)
+        T, dev = x.x.shape[0], x.x.device
+        h1 = torch.empty(T, self.dim, dtype=self.dtype, device=dev)
+        if self.feed_forward is not None:
+            h2 = torch.empty(T, self.dim, dtype=self.dtype, device=dev)
+            self.mixer_norm.forward_with(self.ffn_norm, x, h1, h2)
+        else:
+            self.mixer_norm.forward(x, h1)
+        y1 = Branch(T, self.dim, dev)
+        self.mixer.forward(h1, batch, view, residual=y1, append=append)
+        x.add_scaled(y1, None if self.mixer_scale is None else self.mixer_scale.weight)
+        if self.feed_forward is not None:
+            y2 = Branch(T, self.dim, dev)
+            self.feed_forward.forward(h2, residual=y2)
+            x.add_scaled(y2, None if self.ffn_scale is None else self.ffn_scale.weight)

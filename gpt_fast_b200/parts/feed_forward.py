@@ -39,9 +39,10 @@ class SwiGLU:
 @register_feed_forward("dense")
 class Dense:
     """Two products with a unary activation between them: down(act(up x)).  activation: 'gelu' (the exact one,
-    0.5 z (1 + erf(z / sqrt 2))), 'gelu_tanh' or 'silu'; it is applied in the first product's epilogue."""
+    0.5 z (1 + erf(z / sqrt 2))), 'gelu_tanh', 'silu' or 'relu2' (the square of max(z, 0)); it is applied in the first
+    product's epilogue."""
 
-    ACTIVATIONS = ("gelu", "gelu_tanh", "silu")
+    ACTIVATIONS = ("gelu", "gelu_tanh", "silu", "relu2")
 
     def __init__(self, dim: int, hidden: int, dtype: torch.dtype, activation: str = "gelu"):
         if activation not in self.ACTIVATIONS:

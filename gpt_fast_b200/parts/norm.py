@@ -42,20 +42,25 @@ class LayerNorm:
     (`add_into`: x += mult * norm(y)), which a sandwich block uses behind each sublayer; when the stream still owes
     such a sum as it is normed, one kernel does both."""
 
-    def __init__(self, dim: int, eps: float, dtype: torch.dtype):
-        self.dim, self.eps, self.dtype = dim, float(eps), dtype
+    def __init__(self, dim: int, eps: float, dtype: torch.dtype, bias: bool = True):
+        self.dim, self.eps, self.dtype, self.has_bias = dim, float(eps), dtype, bool(bias)
         self.weight = self.bias = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.dim,), "vector"), "bias": ParamSpec((self.dim,), "vector")}
+        specs = {"weight": ParamSpec((self.dim,), "vector")}
+        if self.has_bias:
+            specs["bias"] = ParamSpec((self.dim,), "vector")
+        return specs
 
     def load(self, tensors):
-        self.weight, self.bias = tensors["weight"], tensors["bias"]
-        if self.bias.dtype != self.weight.dtype:
-            self.bias = self.bias.to(self.weight.dtype)
+        self.weight = tensors["weight"]
+        if self.has_bias:
+            self.bias = tensors["bias"]
+            if self.bias.dtype != self.weight.dtype:
+                self.bias = self.bias.to(self.weight.dtype)
 
     def export(self):
-        return {"weight": self.weight, "bias": self.bias}
+        return {"weight": self.weight, "bias": self.bias} if self.has_bias else {"weight": self.weight}
 
     def _branch_args(self, owed):
         branch, norm, mult = owed
@@ -78,3 +83,20 @@ class LayerNorm:
     def add_into(self, x32, branch, mult: float) -> None:
         """x32 (float32 [T, dim], complete) += mult * norm(branch)."""
         ops.layernorm(x32, None, None, 0.0, None, None, branch=(branch.value(), self.weight, self.bias, self.eps, mult))
+
+    def forward_with(self, other: "LayerNorm", x: Residual, out, other_out):
+        """Two norms of the same rows in one pass: out = self(x), other_out = other(x), from one mean and variance.
+        Scaled branches that the stream still owes (`Residual.add_scaled`) are added by the same kernel.  Both norms
+        are without bias."""
+        if self.has_bias or other.has_bias:
+            raise ValueError("two norms of one row in one kernel: only for norms without bias")
+        owed = x.take_scaled()
+        pending = x.take_pending()
+        if pending is not None:
+            owed = owed + [(pending, None)]
+        if len(owed) > 2:
+            x.scaled = owed[2:]
+            x.resolve()
+            owed = owed[:2]
+        ops.layernorm_multi(x.x, [(b if torch.is_tensor(b) else b.value(), s) for b, s in owed],
+                            [(self.weight, self.eps, out), (other.weight, other.eps, other_out)])

@@ -12,6 +12,7 @@ reads x, which then does both norms in one pass over the row.  Parts use
     residual.add_linear(a, w)        x += a @ w.T   (fused into the product's epilogue, or deferred)
     residual.add(y)                  x += y         (for parts that cannot fuse)
     residual.add_normed(y, norm, m)  x += m * norm(y), y a `Branch`  (deferred to the next norm, or resolved)
+    residual.add_scaled(y, s)        x += s * y, y a `Branch`, s a per-column factor [dim]  (deferred the same way)
     residual.tensor()                x, complete
 
 `Branch` is a stream of its own that starts empty: what a sublayer "adds" to it
@@ -27,8 +28,13 @@ class Residual:
         self.x = x
         self.pending = None
         self.normed = None                 # (Branch, norm part, factor) still to be added
+        self.scaled = []                   # (Branch, per-column factor) still to be added
 
     def resolve(self) -> None:
+        if self.scaled:
+            owed, self.scaled = self.scaled, []
+            for i in range(0, len(owed), 2):
+                ops.layernorm_multi(self.x, [(b.value(), s) for b, s in owed[i:i + 2]])
         if self.normed is not None:
             branch, norm, mult = self.take_normed()
             norm.add_into(self.x, branch, mult)
@@ -52,12 +58,26 @@ class Residual:
         self.resolve()
         self.normed = (branch, norm, float(mult))
 
+    def add_scaled(self, branch: "Branch", scale) -> None:
+        """x += scale * branch (scale: a vector over the columns).  Left to the next norm that reads x."""
+        if self.normed is not None or self.pending is not None:
+            self.resolve()
+        self.scaled.append((branch, scale))
+
+    def take_scaled(self):
+        s, self.scaled = self.scaled, []
+        return s
+
     def take_normed(self):
         n, self.normed = self.normed, None
         return n
 
     def take_pending(self):
-        """The partial sums still owed to x (the caller adds them); a normed branch is added first."""
+        """The partial sums still owed to x (the caller adds them); a normed or scaled branch is added first."""
+        if self.scaled:
+            owed, self.scaled = self.scaled, []
+            for i in range(0, len(owed), 2):
+                ops.layernorm_multi(self.x, [(b.value(), s) for b, s in owed[i:i + 2]])
         if self.normed is not None:
             branch, norm, mult = self.take_normed()
             norm.add_into(self.x, branch, mult)
@@ -101,7 +121,7 @@ class Branch(Residual):
 
     def value(self) -> torch.Tensor:
         """The branch as the norm kernels take it: the complete float32 [T, dim] tensor, or partial sums [S, T, dim]."""
-        if self.partials is not None and self.pending is None and self.normed is None:
+        if self.partials is not None and self.pending is None and self.normed is None and not self.scaled:
             p, self.partials = self.partials, None
             self.empty = True
             return p

@@ -128,6 +128,8 @@ class RandomCheckpoint:
             x = (x * self.jitter).to(self.vector_dtype)
         elif s.init == "unit":
             x = x.to(self.vector_dtype)
+        elif s.init == "conv":
+            x = (x * 0.5).to(self.vector_dtype)
         elif s.init == "embedding":
             x = x.to(self.matrix_dtype)
         else:

@@ -13,7 +13,7 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 class Source:
     """One tensor of the checkpoint.  `init` says how the random-weights mode
     draws it: 'normal' = N(0, std), 'norm' = 1 + N(0, jitter), 'bias' = N(0, jitter), 'unit' (a vector) and
-    'embedding' (a matrix) = N(0, 1)."""
+    'embedding' (a matrix) = N(0, 1), 'conv' (taps of a short convolution) = N(0, 0.5)."""
     name: str
     shape: Tuple[int, ...]
     init: str = "normal"

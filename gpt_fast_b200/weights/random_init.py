@@ -29,7 +29,7 @@ def write_model_folder(folder, config: Union[str, Dict[str, Any]], seed: int, *,
     cfg = config_from_name(config) if isinstance(config, str) else dict(config)
     arch = architecture_for(cfg)
     args = arch.parse(cfg)
-    plan = arch.weight_plan(args)
+    plan = arch.weight_plan(args, None) if arch.shapes_from_checkpoint else arch.weight_plan(args)
     ckpt = RandomCheckpoint(plan, seed, std, jitter, _DTYPES[matrix_dtype], _DTYPES[vector_dtype], gen_device)
     os.makedirs(folder, exist_ok=True)
     tensors = {name: ckpt.get(name, "cpu").contiguous() for name in ckpt.shapes()}

@@ -82,7 +82,7 @@ class PlainOps:
             if rms:
                 return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + e) * w.double()
             dev = v - v.mean(-1, keepdim=True)
-            return dev * torch.rsqrt((dev * dev).mean(-1, keepdim=True) + e) * w.double() + b.double()
+            return dev * torch.rsqrt((dev * dev).mean(-1, keepdim=True) + e) * w.double() + (0 if b is None else b.double())
         if branch is not None:
             y, pw, pb, peps, mult = branch
             if y.dim() == 3:
@@ -91,6 +91,128 @@ class PlainOps:
         if out is not None:
             xr = x if rows is None else x[rows.long()]
             out.copy_(norm(xr, weight, bias, eps).to(out.dtype))
+
+    # -- a hashed bigram embedding, one row with several norms ------------------------------
+    def embed_hashed(self, tokens, table, extra, out, batch, prev, buckets, mul_prev, mul_cur, scale=1.0):
+        ids = tokens.long()
+        pos, slots = token_positions(batch)
+        seq = batch.tok_seq.long()
+        first_of_step = torch.arange(batch.n_tokens) == batch.cu_seqlens.long()[seq]
+        before = torch.where(first_of_step, prev.long()[slots], torch.roll(ids, 1))
+        rows = torch.where(pos == 0, torch.tensor(buckets), (before * mul_prev + ids * mul_cur) % buckets)
+        out.copy_((table[ids].double() * scale + extra[rows].double()).float())
+        last = batch.cu_seqlens.long()[1:] - 1
+        prev[batch.slots.long()] = tokens[last]
+
+    def layernorm_multi(self, x, branches=(), outs=(), rows=None, rms=False):
+        for y, scale in branches:
+            y = y.double().sum(0) if y.dim() == 3 else y.double()
+            x.copy_((x.double() + (y if scale is None else y * scale.double())).float())
+        for w, eps, out in outs:
+            v = (x if rows is None else x[rows.long()]).double()
+            dev = v if rms else v - v.mean(-1, keepdim=True)
+            out.copy_((dev * torch.rsqrt((dev * dev).mean(-1, keepdim=True) + eps) * w.double()).to(out.dtype))
+
+    # -- latent attention ---------------------------------------------------------------------
+    def latent_prepare(self, src, q_off, kv_off, q_out, kv, batch, n_head, head_dim, rot_dim, rank, norm_weight, eps, table,
+                       pairing="interleaved", append=True):
+        T, H, d, r = batch.n_tokens, n_head, head_dim, rot_dim
+        x = src.double()
+        pos, slots = token_positions(batch)
+        cs = table[pos].double()
+        q = x[:, q_off:q_off + H * (d + r)].reshape(T, H, d + r)[..., d:]
+        q_out[..., rank:] = self._rotate_front(q, cs, r, pairing).to(q_out.dtype)
+        if append:
+            lat = x[:, kv_off:kv_off + rank]
+            c = lat * torch.rsqrt((lat * lat).mean(-1, keepdim=True) + eps) * norm_weight.double()
+            kr = self._rotate_front(x[:, kv_off + rank:kv_off + rank + r].reshape(T, 1, r), cs, r, pairing)[:, 0]
+            page = kv.page_table.long()[slots, pos // kv.page_size]
+            if int(page.min()) < 0:
+                raise IndexError("token lands on a page the slot does not hold")
+            kv.k_pool[page, 0, pos % kv.page_size] = torch.cat([c, kr], -1).to(kv.k_pool.dtype)
+
+    def headwise_linear(self, a, w, out, n_head, k, n, a_off=0, a_stride=None, out_off=0, out_stride=None, layout="kn",
+                        gate=None, gate_off=0):
+        a_stride = k if a_stride is None else a_stride
+        out_stride = n if out_stride is None else out_stride
+        for h in range(n_head):
+            x = a[:, a_off + h * a_stride:a_off + h * a_stride + k].double()
+            y = x @ (w[h].double() if layout == "kn" else w[h].double().T)
+            if gate is not None:
+                y = y * torch.sigmoid(gate[:, gate_off + h * n:gate_off + (h + 1) * n].double())
+            out[:, out_off + h * out_stride:out_off + h * out_stride + n] = y.to(out.dtype)
+
+    # -- recurrent mixers -----------------------------------------------------------------------
+    def short_conv(self, src, col_off, channels, weight, bias, state, state_off, out, batch, act=True):
+        taps, C = weight.shape[1], channels
+        w = weight.double()
+        x = src[:, col_off:col_off + C].double()
+        cu = batch.cu_seqlens.tolist()
+        for s in range(batch.n_seqs):
+            slot = int(batch.slots[s])
+            old = state[slot, state_off:state_off + (taps - 1) * C].double().view(taps - 1, C)
+            seq = torch.cat([old, x[cu[s]:cu[s + 1]]])
+            n = cu[s + 1] - cu[s]
+            y = torch.zeros(n, C, dtype=torch.float64)
+            for j in range(taps):
+                y += seq[j:j + n] * w[:, j]
+            if bias is not None:
+                y += bias.double()
+            out[cu[s]:cu[s + 1]] = (y / (1 + torch.exp(-y)) if act else y).float()
+            state[slot, state_off:state_off + (taps - 1) * C] = seq[n:].reshape(-1).float()
+
+    def ssd_scan(self, x, b_off, c_off, dt_src, dt_off, dt_bias, a_log, skip, state, state_off, out, batch, n_head, head_dim,
+                 n_state, n_groups):
+        H, P, N, G = n_head, head_dim, n_state, n_groups
+        T = batch.n_tokens
+        xd = x.double()
+        X = xd[:, :H * P].reshape(T, H, P)
+        B = xd[:, b_off:b_off + G * N].reshape(T, G, N).repeat_interleave(H // G, dim=1)
+        C = xd[:, c_off:c_off + G * N].reshape(T, G, N).repeat_interleave(H // G, dim=1)
+        dt = torch.nn.functional.softplus(dt_src[:, dt_off:dt_off + H].double() + dt_bias.double())
+        decay = torch.exp(-torch.exp(a_log.double()) * dt)
+        _, slots = token_positions(batch)
+        for t in range(T):
+            slot = int(slots[t])
+            S = state[slot, state_off:state_off + H * N * P].double().view(H, N, P)
+            S = decay[t][:, None, None] * S + (dt[t][:, None] * B[t])[:, :, None] * X[t][:, None, :]
+            state[slot, state_off:state_off + H * N * P] = S.reshape(-1).float()
+            y = torch.einsum("hnp,hn->hp", S, C[t])
+            if skip is not None:
+                y = y + skip.double()[:, None] * X[t]
+            out[t] = y.float()
+
+    def delta_rule(self, qkv, offsets, beta_src, beta_off, a_src, a_off, dt_bias, a_log, state, state_off, out, batch, n_head,
+                   n_qk, head_dim, v_head_dim, q_scale, unit_eps=1e-6):
+        H, J, d, dv = n_head, n_qk, head_dim, v_head_dim
+        T = batch.n_tokens
+        x = qkv.double()
+        qo, ko, vo = offsets
+        q = x[:, qo:qo + J * d].reshape(T, J, d)
+        k = x[:, ko:ko + J * d].reshape(T, J, d)
+        v = x[:, vo:vo + H * dv].reshape(T, H, dv)
+        q = (q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * q_scale).repeat_interleave(H // J, dim=1)
+        k = (k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(H // J, dim=1)
+        beta = torch.sigmoid(beta_src[:, beta_off:beta_off + H].double())
+        a = a_src[:, a_off:a_off + H * d].double() + dt_bias.double()
+        g = torch.exp(-torch.exp(a_log.double())[None, :, None] * torch.nn.functional.softplus(a).view(T, H, d))
+        _, slots = token_positions(batch)
+        for t in range(T):
+            slot = int(slots[t])
+            S = g[t][:, :, None] * state[slot, state_off:state_off + H * d * dv].double().view(H, d, dv)
+            u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, k[t]))
+            S = S + k[t][:, :, None] * u[:, None, :]
+            state[slot, state_off:state_off + H * d * dv] = S.reshape(-1).float()
+            out[t] = torch.einsum("hdv,hd->hv", S, q[t]).float()
+
+    def gated_norm(self, y, gate, gate_off, weight, out, group, eps, act="silu", gate_first=False):
+        T, C = y.shape
+        z = gate[:, gate_off:gate_off + C].double()
+        a = torch.sigmoid(z) if act == "sigmoid" else z * torch.sigmoid(z)
+        v = y.double() * a if gate_first else y.double()
+        v = v.view(T, C // group, group)
+        v = (v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)).view(T, C) * weight.double().repeat(C // weight.shape[0])
+        out.copy_((v if gate_first else v * a).to(out.dtype))
 
     @staticmethod
     def _rotate_front(v, cs, rot_dims, pairing):
@@ -168,15 +290,17 @@ class PlainOps:
             return 0.5 * z * (1 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
         if kind == "silu":
             return z / (1 + torch.exp(-z))
+        if kind == "relu2":
+            return torch.clamp(z, min=0) ** 2
         raise ValueError(kind)
 
     def activation(self, x, kind, out=None):
         (x if out is None else out).copy_(self._unary(x.double(), kind).to(x.dtype))
 
-    def rope_table(self, inv_freq, table):
+    def rope_table(self, inv_freq, table, amplitude=1.0):
         ang = torch.arange(table.shape[0], dtype=torch.float32, device=table.device)[:, None] * inv_freq[None, :]
-        table[..., 0] = torch.cos(ang.double()).float()
-        table[..., 1] = torch.sin(ang.double()).float()
+        table[..., 0] = (torch.cos(ang.double()) * amplitude).float()
+        table[..., 1] = (torch.sin(ang.double()) * amplitude).float()
 
     def add_partials(self, x, pending):
         x.copy_((x.double() + pending.double().sum(0)).float())
@@ -232,13 +356,14 @@ class PlainOps:
         elif mode == "swiglu":
             g, u = acc[:, 0::2], acc[:, 1::2]
             out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
-        elif mode in ("gelu", "gelu_tanh", "silu"):
+        elif mode in ("gelu", "gelu_tanh", "silu", "relu2"):
             out.copy_(self._unary(acc, mode).to(out.dtype))
         else:
             raise ValueError(mode)
 
     # -- attention -----------------------------------------------------------------------
-    def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None):
+    def attention(self, q, kv, batch, out, n_head, n_kv, head_dim, scale, window=None, chunk=None, sink=None, v_head_dim=None,
+                  values_in_keys=False):
         H, G, d = n_head, n_kv, head_dim
         dv = v_head_dim or head_dim
         pos, slots = token_positions(batch)
@@ -254,7 +379,7 @@ class PlainOps:
             if int(pages.min()) < 0:
                 raise IndexError("attention reads a page the slot does not hold")
             k = kv.k_pool[pages, :, j % kv.page_size].double()      # [n, G, d]
-            v = kv.v_pool[pages, :, j % kv.page_size].double()
+            v = k[..., :dv] if values_in_keys else kv.v_pool[pages, :, j % kv.page_size].double()
             k = k.repeat_interleave(rep, dim=1)
             v = v.repeat_interleave(rep, dim=1)
             s = torch.einsum("hd,nhd->hn", q[t].double(), k) * scale

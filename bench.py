@@ -370,29 +370,36 @@ def design_bench(a, design):
     import gpt_fast_b200 as gf
     from gpt_fast_b200 import ops
     from gpt_fast_b200.config.registry import config_from_name
-    if design != "lasezen":
+    # design -> [(named size, layers to build or None for all, the model beside it: a label and a config from the size's own)]
+    tables = {"lasezen": [("lasezen-1b", None, "llama", llama_twin), ("lasezen-7b", a.layers or 8, "llama", llama_twin)],
+              # beside Gikepel: the library's other hybrid of attention and a recurrent mixer, at the same width, depth,
+              # feed-forward size and vocabulary
+              "gikepel": [("gikepel-1b", a.layers, "lasezen", lambda cfg: dict(config_from_name("lasezen-1b"),
+                                                                               layers=config_from_name("lasezen-1b")["layers"][:len(cfg["layers"])]))]}
+    if design not in tables:
         print(f"bench.py: no size table for design '{design}'")
         return 2
     torch.cuda.set_device(0)
     pk = peaks()
     out = {"design": design, "dtype": "bf16", "data": "synthetic", "peaks": pk, "sizes": []}
+    lengths = tuple(int(x) for x in a.prefill_lengths.split(",")) if a.prefill_lengths else (512, 2048, 8192)
     with ClockSampler() as clocks:
-        for name, n_layers in (("lasezen-1b", None), ("lasezen-7b", a.layers or 8)):
+        for name, n_layers, twin_label, twin in tables[design]:
             cfg = config_from_name(name)
             if n_layers:
                 cfg["layers"] = cfg["layers"][:n_layers]
             row = {"size": name, "layers": len(cfg["layers"]), "width": cfg["width"]}
-            for label, source in ((design, cfg), ("llama", llama_twin(cfg))):
+            for label, source in ((design, cfg), (twin_label, twin(cfg))):
                 model = gf.load(source, dtype="bfloat16", device="cuda:0", random_weights=True, seed=0)
                 r = {"weight_gb": round(model.weight_bytes() / 1e9, 3)}
-                r["prefill_ms"] = {str(T): round(prefill_bench(gf, torch, model, T), 3) for T in (512, 2048, 8192)}
+                r["prefill_ms"] = {str(T): round(prefill_bench(gf, torch, model, T), 3) for T in lengths}
                 r["prefill_tok_s"] = {T: round(int(T) / ms * 1e3) for T, ms in r["prefill_ms"].items()}
                 r["decode_ms"], r["decode_tok_s"] = {}, {}
                 for batch in (1, 8, 64):
                     prompts = random_prompts(torch, model.vocab_size, [512] * batch, 3)
                     ms = decode_bench(gf, torch, model, prompts, 2048, a.steps, a.warmup)[0]
                     r["decode_ms"][str(batch)], r["decode_tok_s"][str(batch)] = round(ms, 4), round(batch / ms * 1e3)
-                r["prefill_shares_ms"] = step_shares(gf, torch, ops, model, random_prompts(torch, model.vocab_size, [2048], 4), False)
+                r["prefill_shares_ms"] = step_shares(gf, torch, ops, model, random_prompts(torch, model.vocab_size, [min(2048, max(lengths))], 4), False)
                 r["decode_shares_ms"] = step_shares(gf, torch, ops, model, random_prompts(torch, model.vocab_size, [512] * 8, 5), True)
                 row[label] = r
                 del model
@@ -425,7 +432,8 @@ def main():
     ap.add_argument("--skip-configs", action="store_true", help="leave out the Llama-3.2-3B and Llama-2-13B sizes")
     ap.add_argument("--skip-shares", action="store_true", help="leave out the per-kernel shares")
     ap.add_argument("--design", default=None, help="instead of the default workload: prefill and decode of another design "
-                    "(lasezen) at layer sizes of a real model, beside the Llama decoder at equal size")
+                    "(lasezen, gikepel) at layer sizes of a real model, beside the library's closest other model at equal size")
+    ap.add_argument("--prefill-lengths", default=None, help="with --design: prompt lengths of the prefill rows (default 512,2048,8192)")
     a = ap.parse_args()
     if a.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {a.gpus} is not supported")

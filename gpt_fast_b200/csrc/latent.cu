@@ -9,8 +9,9 @@
 // gfb_latent_prepare   per token: c = rms_norm(first `rank` outputs of the down projection) * weight, the last
 //                      `rot` outputs rotated by the token's position; both appended to the cache as one row;
 //                      every head's rotated query part turned and written behind the head's latent query.
-// gfb_headwise_linear  out[t, h, :] = W_h in[t, h, :] with a weight per head (the two expansions above), strided
+// gfb_headwise_linear  out[t, h, :] = in[t, h, :] W_h with a weight per head (the two expansions above), strided
 //                      inputs and outputs, optionally times sigmoid(gate[t, h, :]).
+// gfb_latent_attention attention on the cached rows for bfloat16 on tensor cores (below).
 // Norm, angles and rotation are 32-bit; sums are 32-bit in a fixed order.
 #include "common.cuh"
 
@@ -110,18 +111,22 @@ GFB_API int gfb_latent_prepare(const void* src, int dt, int ld, int q_off, int k
 }
 
 // ---------------------------------------------------------------- a product with a weight per head -----
-// out[t, h, n] = sum_k in[t, h, k] * W_h[k, n]  (kn = 1: W stored [H][K][N])  or  W_h[n, k]  (kn = 0: [H][N][K]),
-// optionally times sigmoid(gate[t, h * N + n]).  A block takes TT tokens of one head; the inputs sit in shared
-// memory as 32-bit numbers; a thread owns output columns and adds over k in ascending order.
+// out[t, h, n] = sum_k in[t, h, k] * W_h[k, n]  (W stored [H][K][N]), optionally times sigmoid(gate[t, h * N + n]).
+// A block takes HL_TT tokens of one head and 128 output columns; its inputs sit in shared memory as 32-bit numbers.
+// Thread (column, slice) adds every HL_KS-th k in ascending order (the weight loads of a warp are one row piece,
+// coalesced); the slices' sums are then added in ascending order through shared memory.
 constexpr int HL_TT = 8;
-constexpr int HL_THREADS = 128;
+constexpr int HL_COLS = 128;
+constexpr int HL_KS = 4;
+constexpr int HL_THREADS = HL_COLS * HL_KS;
 
 template <typename T>
 __global__ void __launch_bounds__(HL_THREADS)
-headwise_linear_kernel(const T* __restrict__ in, int ld_in, int in_off, int in_stride, const T* __restrict__ w, int kn,
+headwise_linear_kernel(const T* __restrict__ in, int ld_in, int in_off, int in_stride, const T* __restrict__ w,
                        T* __restrict__ out, int ld_out, int out_off, int out_stride, const T* __restrict__ gate, int ld_gate,
                        int gate_off, int n_tokens, int K, int N) {
-    extern __shared__ float xs[];                 // [HL_TT][K]
+    extern __shared__ float xs[];                 // [HL_TT][K], then [HL_KS][HL_TT][HL_COLS] partial sums
+    float* part = xs + (size_t)HL_TT * K;
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int h = blockIdx.y;
@@ -132,63 +137,45 @@ headwise_linear_kernel(const T* __restrict__ in, int ld_in, int in_off, int in_s
         xs[i] = tt < nt ? gfb_to_f32(in[(size_t)(t0 + tt) * ld_in + in_off + (size_t)h * in_stride + k]) : 0.f;
     }
     __syncthreads();
+    const int c = threadIdx.x % HL_COLS, ks = threadIdx.x / HL_COLS;
+    const int n = blockIdx.z * HL_COLS + c;
     const T* wh = w + (size_t)h * K * N;
-    if (kn) {
-        for (int n = threadIdx.x; n < N; n += blockDim.x) {
-            float acc[HL_TT];
+    float acc[HL_TT];
 #pragma unroll
-            for (int tt = 0; tt < HL_TT; tt++) acc[tt] = 0.f;
-            for (int k = 0; k < K; k++) {
-                const float wv = gfb_to_f32(wh[(size_t)k * N + n]);
+    for (int tt = 0; tt < HL_TT; tt++) acc[tt] = 0.f;
+    if (n < N) {
+#pragma unroll 4
+        for (int k = ks; k < K; k += HL_KS) {
+            const float wv = gfb_to_f32(wh[(size_t)k * N + n]);
 #pragma unroll
-                for (int tt = 0; tt < HL_TT; tt++) acc[tt] = fmaf(xs[tt * K + k], wv, acc[tt]);
-            }
-#pragma unroll
-            for (int tt = 0; tt < HL_TT; tt++)
-                if (tt < nt) {
-                    float v = acc[tt];
-                    if (gate != nullptr) v *= 1.0f / (1.0f + expf(-gfb_to_f32(gate[(size_t)(t0 + tt) * ld_gate + gate_off + (size_t)h * N + n])));
-                    out[(size_t)(t0 + tt) * ld_out + out_off + (size_t)h * out_stride + n] = gfb_from_f32<T>(v);
-                }
+            for (int tt = 0; tt < HL_TT; tt++) acc[tt] = fmaf(xs[tt * K + k], wv, acc[tt]);
         }
-    } else {
-        // a warp per output column: lanes stride over k, then a fixed tree adds the 32 partial sums
-        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-        for (int n = warp; n < N; n += nwarp) {
-            float acc[HL_TT];
+    }
 #pragma unroll
-            for (int tt = 0; tt < HL_TT; tt++) acc[tt] = 0.f;
-            for (int k = lane; k < K; k += 32) {
-                const float wv = gfb_to_f32(wh[(size_t)n * K + k]);
+    for (int tt = 0; tt < HL_TT; tt++) part[((size_t)ks * HL_TT + tt) * HL_COLS + c] = acc[tt];
+    __syncthreads();
+    for (int i = threadIdx.x; i < HL_TT * HL_COLS; i += blockDim.x) {
+        const int tt = i / HL_COLS, cc = i - tt * HL_COLS, col = blockIdx.z * HL_COLS + cc;
+        if (tt >= nt || col >= N) continue;
+        float v = part[(size_t)tt * HL_COLS + cc];
 #pragma unroll
-                for (int tt = 0; tt < HL_TT; tt++) acc[tt] = fmaf(xs[tt * K + k], wv, acc[tt]);
-            }
-#pragma unroll
-            for (int tt = 0; tt < HL_TT; tt++) acc[tt] = gfb_warp_sum(acc[tt]);
-            if (lane == 0) {
-#pragma unroll
-                for (int tt = 0; tt < HL_TT; tt++)
-                    if (tt < nt) {
-                        float v = acc[tt];
-                        if (gate != nullptr) v *= 1.0f / (1.0f + expf(-gfb_to_f32(gate[(size_t)(t0 + tt) * ld_gate + gate_off + (size_t)h * N + n])));
-                        out[(size_t)(t0 + tt) * ld_out + out_off + (size_t)h * out_stride + n] = gfb_from_f32<T>(v);
-                    }
-            }
-        }
+        for (int s = 1; s < HL_KS; s++) v += part[((size_t)s * HL_TT + tt) * HL_COLS + cc];
+        if (gate != nullptr) v *= 1.0f / (1.0f + expf(-gfb_to_f32(gate[(size_t)(t0 + tt) * ld_gate + gate_off + (size_t)h * N + col])));
+        out[(size_t)(t0 + tt) * ld_out + out_off + (size_t)h * out_stride + col] = gfb_from_f32<T>(v);
     }
 }
 
-// in [T, ld_in]: head h's K inputs start at column in_off + h * in_stride; out [T, ld_out] likewise; w [H, K, N] (kn)
-// or [H, N, K]; gate (or null) [T, ld_gate] with head h's N gate values at column gate_off + h * N.  One type for all.
-GFB_API int gfb_headwise_linear(const void* in, int dt, int ld_in, int in_off, int in_stride, const void* w, int kn, void* out,
+// in [T, ld_in]: head h's K inputs start at column in_off + h * in_stride; out [T, ld_out] likewise; w [H, K, N]; gate (or
+// null) [T, ld_gate] with head h's N gate values at column gate_off + h * N.  One type for all.
+GFB_API int gfb_headwise_linear(const void* in, int dt, int ld_in, int in_off, int in_stride, const void* w, void* out,
                                 int ld_out, int out_off, int out_stride, const void* gate, int ld_gate, int gate_off,
                                 int n_tokens, int H, int K, int N, cudaStream_t stream) {
     if (n_tokens <= 0 || H <= 0 || N <= 0) return 0;
     if (K <= 0) return gfb_fail("gfb_headwise_linear: K = %d", K);
-    if (H > 65535) return gfb_fail("gfb_headwise_linear: %d heads exceed the grid limit", H);
-    const size_t smem = (size_t)HL_TT * K * sizeof(float);
+    if (H > 65535 || (N + HL_COLS - 1) / HL_COLS > 65535) return gfb_fail("gfb_headwise_linear: %d heads of %d columns exceed the grid limit", H, N);
+    const size_t smem = ((size_t)HL_TT * K + (size_t)HL_KS * HL_TT * HL_COLS) * sizeof(float);
     if (smem > 160 * 1024) return gfb_fail("gfb_headwise_linear: K = %d does not fit shared memory", K);
-    dim3 grid((n_tokens + HL_TT - 1) / HL_TT, H);
+    dim3 grid((n_tokens + HL_TT - 1) / HL_TT, H, (N + HL_COLS - 1) / HL_COLS);
     cudaError_t e;
 #define GO(T)                                                                                                               \
     do {                                                                                                                    \
@@ -198,11 +185,236 @@ GFB_API int gfb_headwise_linear(const void* in, int dt, int ld_in, int in_off, i
             allowed = 160 * 1024;                                                                                           \
         }                                                                                                                   \
         e = gfb_launch(headwise_linear_kernel<T>, grid, dim3(HL_THREADS), smem, stream, (const T*)in, ld_in, in_off, in_stride, \
-                       (const T*)w, kn, (T*)out, ld_out, out_off, out_stride, (const T*)gate, ld_gate, gate_off, n_tokens, K, N); \
+                       (const T*)w, (T*)out, ld_out, out_off, out_stride, (const T*)gate, ld_gate, gate_off, n_tokens, K, N); \
     } while (0)
     if (dt == GFB_BF16) GO(__nv_bfloat16);
     else if (dt == GFB_F32) GO(float);
     else return gfb_fail("gfb_headwise_linear: unknown type %d", dt);
 #undef GO
     return gfb_check(e, "gfb_headwise_linear");
+}
+
+// ---------------------------------------------------------------- attention on the latent, many queries ----
+// All heads read the same cached rows: keys are the whole rows (Dk = rank + rot numbers), values their first `rank`
+// numbers.  So the rows of one MMA are (token, head) pairs of ONE sequence, 64 of them per block (four warps of 16),
+// and a tile of 32 cached rows, fetched once into shared memory (cp.async, two stages), serves as the B operand of
+// S = Q K^T (as stored) and of O += P V (transposed on the way into the registers).  The value columns are split
+// between two warps per 16 query rows (each computes the same scores and keeps half of O in registers: 128 numbers
+// per thread at rank 512).  bfloat16 operands on `mma.sync.m16n8k16`, scores, softmax and sums in 32-bit; the softmax
+// weights are rounded to bfloat16 for the second product.  Keys are masked per row by the row's own position.
+constexpr int LA_ROWS = 64;           // query rows per block
+constexpr int LA_KEYS = 32;           // cached rows per tile
+constexpr int LA_THREADS = 256;
+constexpr int LA_PAD = 8;             // bfloat16 numbers of padding per shared-memory row: ldmatrix rows fall into distinct banks
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// NT: value n-tiles (of 8 columns) a warp may hold: rank / 2 <= 8 * NT
+template <int NT>
+__global__ void __launch_bounds__(LA_THREADS, 1)
+latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, GfbPagedKV kv, GfbBatch b,
+                        int H, int Dk, int R, float scale_log2, int* status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int DkP = Dk + LA_PAD;
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [LA_ROWS][DkP]
+    __nv_bfloat16* sK = sQ + (size_t)LA_ROWS * DkP;                             // [2][LA_KEYS][DkP]
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int s = blockIdx.x;
+    const int t0 = b.cu_seqlens[s], n_rows = (b.cu_seqlens[s + 1] - t0) * H;
+    const int m0 = blockIdx.y * LA_ROWS;
+    if (m0 >= n_rows) return;
+    const int slot = b.slots[s], start = b.lengths[slot];
+    const int rows_here = min(LA_ROWS, n_rows - m0);
+    const int last_pos = start + (m0 + rows_here - 1) / H;                      // the latest position any row of the block sees
+    const int n_tiles = last_pos / LA_KEYS + 1;
+    const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int chunks = Dk / 8;                                                  // 16-byte pieces of a row
+
+    auto load_keys = [&](int stage, int tile) {
+        const int key0 = tile * LA_KEYS;
+        const int pi = key0 / kv.page_size;
+        int page = pi < kv.max_pages ? pt[pi] : -1;
+        if (page < 0 || page >= kv.n_pages) {
+            if (tid == 0) gfb_report(status, GFB_ERR_PAGE_TABLE, slot, pi);
+            page = 0;
+        }
+        const __nv_bfloat16* src = (const __nv_bfloat16*)kv.k_pool + ((size_t)page * kv.page_size + key0 % kv.page_size) * Dk;
+        __nv_bfloat16* dst = sK + (size_t)stage * LA_KEYS * DkP;
+        for (int c = tid; c < LA_KEYS * chunks; c += LA_THREADS) {
+            const int r = c / chunks, cc = c - r * chunks;
+            cp_async16(dst + (size_t)r * DkP + cc * 8, src + (size_t)r * Dk + cc * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    load_keys(0, 0);
+    // the block's query rows (rows beyond the sequence's are zero)
+    const __nv_bfloat16* qsrc = q + ((size_t)t0 * H + m0) * Dk;
+    for (int c = tid; c < LA_ROWS * chunks; c += LA_THREADS) {
+        const int r = c / chunks, cc = c - r * chunks;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows_here) v = *reinterpret_cast<const uint4*>(qsrc + (size_t)r * Dk + cc * 8);
+        *reinterpret_cast<uint4*>(sQ + (size_t)r * DkP + cc * 8) = v;
+    }
+
+    const int rw = (warp & 3) * 16;                    // the warp's 16 query rows
+    const int half = warp >> 2;                        // which half of the value columns it keeps
+    const int nt_all = R / 8, nt_lo = half == 0 ? 0 : (nt_all + 1) / 2, nt_n = half == 0 ? (nt_all + 1) / 2 : nt_all - (nt_all + 1) / 2;
+    const int r0 = rw + (lane >> 2);                   // rows of this thread's accumulator values: r0 and r0 + 8
+    const int pos0 = (r0 < rows_here) ? start + (m0 + r0) / H : -1, pos1 = (r0 + 8 < rows_here) ? start + (m0 + r0 + 8) / H : -1;
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float mx0 = -INFINITY, mx1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    for (int tile = 0; tile < n_tiles; tile++) {
+        const int stage = tile & 1;
+        if (tile + 1 < n_tiles) {
+            load_keys(stage ^ 1, tile + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const __nv_bfloat16* kt = sK + (size_t)stage * LA_KEYS * DkP;
+        // scores of 16 rows x 32 keys
+        float sc[LA_KEYS / 8][4];
+#pragma unroll
+        for (int j = 0; j < LA_KEYS / 8; j++) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+        for (int kk = 0; kk < Dk; kk += 16) {
+            uint32_t a[4];
+            ldsm_x4(a, sQ + (size_t)(rw + (lane & 7) + 8 * ((lane >> 3) & 1)) * DkP + kk + 8 * (lane >> 4));
+#pragma unroll
+            for (int j = 0; j < LA_KEYS / 8; j += 2) {
+                uint32_t bb[4];
+                ldsm_x4(bb, kt + (size_t)((j + (lane >> 4)) * 8 + (lane & 7)) * DkP + kk + 8 * ((lane >> 3) & 1));
+                mma_bf16(sc[j], a, bb[0], bb[1]);
+                mma_bf16(sc[j + 1], a, bb[2], bb[3]);
+            }
+        }
+        // mask by each row's position, running maximum and sum
+        const int key0 = tile * LA_KEYS + 2 * (lane & 3);
+        float t0m = -INFINITY, t1m = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < LA_KEYS / 8; j++) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int key = key0 + j * 8 + e;
+                sc[j][e] = key <= pos0 ? sc[j][e] * scale_log2 : -INFINITY;
+                sc[j][2 + e] = key <= pos1 ? sc[j][2 + e] * scale_log2 : -INFINITY;
+                t0m = fmaxf(t0m, sc[j][e]);
+                t1m = fmaxf(t1m, sc[j][2 + e]);
+            }
+        }
+        t0m = fmaxf(t0m, __shfl_xor_sync(0xffffffffu, t0m, 1));
+        t0m = fmaxf(t0m, __shfl_xor_sync(0xffffffffu, t0m, 2));
+        t1m = fmaxf(t1m, __shfl_xor_sync(0xffffffffu, t1m, 1));
+        t1m = fmaxf(t1m, __shfl_xor_sync(0xffffffffu, t1m, 2));
+        const float n0 = fmaxf(mx0, t0m), n1 = fmaxf(mx1, t1m);
+        const float u0 = n0 == -INFINITY ? 0.f : n0, u1 = n1 == -INFINITY ? 0.f : n1;       // a row that sees nothing yet
+        const float al0 = exp2f(mx0 - u0), al1 = exp2f(mx1 - u1);                             // exp2(-inf) = 0
+        mx0 = n0;
+        mx1 = n1;
+        float s0 = 0.f, s1 = 0.f;
+        uint32_t pa[LA_KEYS / 16][4];
+#pragma unroll
+        for (int j = 0; j < LA_KEYS / 8; j++) {
+            const float p00 = exp2f(sc[j][0] - u0), p01 = exp2f(sc[j][1] - u0), p10 = exp2f(sc[j][2] - u1), p11 = exp2f(sc[j][3] - u1);
+            s0 += p00 + p01;
+            s1 += p10 + p11;
+            pa[j >> 1][(j & 1) * 2] = pack_bf16(p00, p01);
+            pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p10, p11);
+        }
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+        l0 = l0 * al0 + s0;
+        l1 = l1 * al1 + s1;
+        // O = O * alpha + P V over the warp's value columns
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+            o[j][0] *= al0; o[j][1] *= al0; o[j][2] *= al1; o[j][3] *= al1;
+        }
+#pragma unroll
+        for (int kb = 0; kb < LA_KEYS / 16; kb++) {
+#pragma unroll
+            for (int j = 0; j < NT; j += 2) {
+                if (j < nt_n) {
+                    // the second tile of the pair may lie beyond the warp's columns (an odd count): it reads the next
+                    // columns of the row, which exist (Dk > R), and its result is dropped
+                    uint32_t vb[4];
+                    ldsm_x4_trans(vb, kt + (size_t)(kb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * DkP + (nt_lo + j + (lane >> 4)) * 8);
+                    mma_bf16(o[j], pa[kb], vb[0], vb[1]);
+                    if (j + 1 < NT) mma_bf16(o[j + 1], pa[kb], vb[2], vb[3]);
+                }
+            }
+        }
+        __syncthreads();                               // the stage is free for the tile after next
+    }
+    const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+    __nv_bfloat16* orow = out + ((size_t)t0 * H + m0) * R;
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        if (j < nt_n) {
+            const int col = (nt_lo + j) * 8 + 2 * (lane & 3);
+            if (r0 < rows_here) *reinterpret_cast<uint32_t*>(orow + (size_t)r0 * R + col) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
+            if (r0 + 8 < rows_here) *reinterpret_cast<uint32_t*>(orow + (size_t)(r0 + 8) * R + col) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
+        }
+    }
+}
+
+// q bfloat16 [T, H, Dk] (Dk = rank + rot), out bfloat16 [T, H * rank]; the cache entry holds one row of Dk numbers per
+// token in pages of a multiple of 32 tokens.  Needs Dk % 16 == 0, rank % 16 == 0, rank <= 512, rank < Dk.
+GFB_API int gfb_latent_attention(const void* q, void* out, void* k_pool, const int* page_table, int max_pages, int page_size,
+                                 int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths,
+                                 int n_seqs, int n_tokens, int max_q_len, int H, int Dk, int R, float scale, int* status,
+                                 cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (Dk % 16 || R % 16 || R > 512 || R >= Dk || page_size % LA_KEYS)
+        return gfb_fail("gfb_latent_attention: rows of %d with %d value columns in pages of %d do not fit the kernel", Dk, R, page_size);
+    if ((((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_pool) & 15) != 0) return gfb_fail("gfb_latent_attention: operands must be 16-byte aligned");
+    GfbPagedKV kv{k_pool, nullptr, page_table, max_pages, page_size, n_pages};
+    GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
+    const size_t smem = (size_t)(LA_ROWS + 2 * LA_KEYS) * (Dk + LA_PAD) * sizeof(__nv_bfloat16);
+    if (smem > 220 * 1024) return gfb_fail("gfb_latent_attention: rows of %d numbers do not fit shared memory", Dk);
+    const long tiles = ((long)max_q_len * H + LA_ROWS - 1) / LA_ROWS;
+    if (tiles > 65535) return gfb_fail("gfb_latent_attention: %ld row tiles exceed the grid limit", tiles);
+    dim3 grid(n_seqs, (unsigned)tiles);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const int nt = (R / 8 + 1) / 2;
+    cudaError_t e;
+#define GO(NT)                                                                                                              \
+    do {                                                                                                                    \
+        e = cudaFuncSetAttribute(latent_attention_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+        if (e != cudaSuccess) return gfb_fail("gfb_latent_attention: %s", cudaGetErrorString(e));                           \
+        e = gfb_launch(latent_attention_kernel<NT>, grid, dim3(LA_THREADS), smem, stream, (const __nv_bfloat16*)q,          \
+                       (__nv_bfloat16*)out, kv, b, H, Dk, R, scale_log2, status);                                           \
+    } while (0)
+    if (nt <= 8) GO(8);
+    else if (nt <= 16) GO(16);
+    else GO(32);
+#undef GO
+    return gfb_check(e, "gfb_latent_attention");
 }

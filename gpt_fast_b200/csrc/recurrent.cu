@@ -11,10 +11,10 @@
 // gfb_gated_norm    root-mean-square norm over groups of columns with a weight and a gate (SiLU or sigmoid) that
 //                   is applied before or behind the norm
 //
-// The two recurrences share one layout: a block owns one (sequence, head) and walks through the sequence's
-// tokens of this step; thread (column p, row group r) keeps RPT rows of column p of S in registers.  Sums over
-// the rows are added per thread in ascending order and then over the row groups in ascending order, so a
-// token's result is the same bits however the sequence was cut into steps or batched.  Everything is 32-bit.
+// The two recurrences share one layout: a block owns one (sequence, head) and a slice of the state's columns and
+// walks through the sequence's tokens of this step; a lane keeps RPT rows of one column of S in registers.  Sums
+// over the rows are added per lane in ascending order and then over the lanes of the column in a fixed butterfly, so
+// a token's result is the same bits however the sequence was cut into steps or batched.  Everything is 32-bit.
 #include "common.cuh"
 
 GFB_DEFINE_LAST_ERROR()
@@ -109,58 +109,65 @@ GFB_API int gfb_short_conv(const void* src, int dt, int ld, int col_off, int C, 
 }
 
 // ------------------------------------------------------------------------------ the two recurrences ----
-constexpr int TB = 8;                 // tokens whose inputs are staged in shared memory together
+// Layout of both: the state of a head is rows x columns (rows: state or key channels; columns: value channels); its
+// columns evolve independently, so a block takes one (sequence, head) and a slice of the columns and walks through
+// the sequence's tokens of this step.  The rows are dealt in groups of RPT to RG lanes of a warp (RG a power of two),
+// a warp holds 32 / RG columns, a block four warps.  A sum over the rows is RPT terms per lane in ascending order and
+// then a butterfly over the RG lanes: no barrier per token.  The inputs of TB tokens are staged in shared memory at a
+// time (row vectors padded by one number per group so that the RG lanes read distinct banks).
+constexpr int TB = 16;
+constexpr int SCAN_WARPS = 4;
 
-// sum over the row groups, ascending: part [RG][P] -> the column's total
-__device__ __forceinline__ float sum_groups(const float* part, int RG, int P, int p) {
-    float v = part[p];
-    for (int r = 1; r < RG; r++) v += part[(size_t)r * P + p];
+__device__ __forceinline__ float group_sum(float v, int RG) {
+    for (int o = RG >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+__device__ __forceinline__ int padded(int c, int RPT) { return c + c / RPT; }      // index of row c in a padded row vector
 
 // x [T, ldx] float32: head h's P inputs at column h * P, group g's N numbers of B at b_off + g * N, of C at
 // c_off + g * N.  dt_raw: [T, ld_dt] of type TD, head h at column dt_off + h.
 template <typename TD, int RPT>
-__global__ void __launch_bounds__(RPT == 16 ? 1024 : RPT == 128 ? 256 : 512)
+__global__ void __launch_bounds__(32 * SCAN_WARPS)
 ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, const TD* __restrict__ dt_raw, int ld_dt,
-                                int dt_off, const void* __restrict__ dt_bias, const void* __restrict__ a_log,
-                                const void* __restrict__ skip, int w_dt, float* __restrict__ state, size_t state_ld,
-                                float* __restrict__ out, GfbBatch b, int H, int P, int N, int G) {
+                int dt_off, const void* __restrict__ dt_bias, const void* __restrict__ a_log, const void* __restrict__ skip,
+                int w_dt, float* __restrict__ state, size_t state_ld, float* __restrict__ out, GfbBatch b, int H, int P, int N,
+                int G, int RG) {
     extern __shared__ float sm[];
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int s = blockIdx.x, h = blockIdx.y, g = h / (H / G);
-    const int RG = (N + RPT - 1) / RPT;
-    float* sB = sm;                       // [TB][N]
-    float* sC = sB + TB * N;              // [TB][N]
-    float* sX = sC + TB * N;              // [TB][P]
-    float* sDt = sX + TB * P;             // [TB]
+    const int CW = 32 / RG, CB = SCAN_WARPS * CW, NP = RG * (RPT + 1);
+    float* sB = sm;                       // [TB][NP]
+    float* sC = sB + TB * NP;             // [TB][NP]
+    float* sX = sC + TB * NP;             // [TB][CB]
+    float* sO = sX + TB * CB;             // [TB][CB]
+    float* sDt = sO + TB * CB;            // [TB]
     float* sA = sDt + TB;                 // [TB]
-    float* part = sA + TB;                // [TB][RG][P]
-    const int tid = threadIdx.x;
-    const bool active = tid < P * RG;
-    const int p = active ? tid % P : 0, rg = active ? tid / P : 0;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rgi = lane % RG, cl = warp * CW + lane / RG;           // row group, column within the block
+    const int p0 = blockIdx.z * CB, p = p0 + cl;
+    const bool active = p < P;
     const int t0 = b.cu_seqlens[s], t1 = b.cu_seqlens[s + 1];
     float* S = state + (size_t)b.slots[s] * state_ld + (size_t)h * N * P;
     float st[RPT];
 #pragma unroll
     for (int r = 0; r < RPT; r++) {
-        const int n = rg * RPT + r;
+        const int n = rgi * RPT + r;
         st[r] = (active && n < N) ? S[(size_t)n * P + p] : 0.f;
     }
     const float bias = ldw(dt_bias, w_dt, h), rate = expf(ldw(a_log, w_dt, h)), dskip = skip != nullptr ? ldw(skip, w_dt, h) : 0.f;
     for (int tile = t0; tile < t1; tile += TB) {
         const int nt = min(TB, t1 - tile);
-        __syncthreads();                                       // the previous tile's reads are done
-        for (int i = tid; i < nt * N; i += blockDim.x) {
-            const int tt = i / N, n = i - tt * N;
+        __syncthreads();                                       // the previous tile's outputs are written
+        for (int i = tid; i < nt * RG * RPT; i += blockDim.x) {
+            const int tt = i / (RG * RPT), n = i - tt * RG * RPT;
             const float* row = x + (size_t)(tile + tt) * ldx;
-            sB[tt * N + n] = row[b_off + g * N + n];
-            sC[tt * N + n] = row[c_off + g * N + n];
+            sB[tt * NP + padded(n, RPT)] = n < N ? row[b_off + g * N + n] : 0.f;
+            sC[tt * NP + padded(n, RPT)] = n < N ? row[c_off + g * N + n] : 0.f;
         }
-        for (int i = tid; i < nt * P; i += blockDim.x) {
-            const int tt = i / P, q = i - tt * P;
-            sX[tt * P + q] = x[(size_t)(tile + tt) * ldx + (size_t)h * P + q];
+        for (int i = tid; i < nt * CB; i += blockDim.x) {
+            const int tt = i / CB, q = i - tt * CB;
+            sX[tt * CB + q] = p0 + q < P ? x[(size_t)(tile + tt) * ldx + (size_t)h * P + p0 + q] : 0.f;
         }
         if (tid < nt) {
             const float d = softplus_f(gfb_to_f32(dt_raw[(size_t)(tile + tid) * ld_dt + dt_off + h]) + bias);
@@ -168,31 +175,29 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
             sA[tid] = expf(-rate * d);
         }
         __syncthreads();
-        if (active) {
-            for (int tt = 0; tt < nt; tt++) {
-                const float a = sA[tt], dx = sDt[tt], xp = sX[tt * P + p];
-                float acc = 0.f;
+        for (int tt = 0; tt < nt; tt++) {
+            const float a = sA[tt], dx = sDt[tt], xp = sX[tt * CB + cl];
+            const float* bb = sB + tt * NP + rgi * (RPT + 1);
+            const float* cc = sC + tt * NP + rgi * (RPT + 1);
+            float acc = 0.f;
 #pragma unroll
-                for (int r = 0; r < RPT; r++) {
-                    const int n = rg * RPT + r;
-                    if (n < N) {
-                        st[r] = fmaf(a, st[r], (dx * sB[tt * N + n]) * xp);
-                        acc = fmaf(st[r], sC[tt * N + n], acc);
-                    }
-                }
-                part[((size_t)tt * RG + rg) * P + p] = acc;
+            for (int r = 0; r < RPT; r++) {
+                st[r] = fmaf(a, st[r], (dx * bb[r]) * xp);
+                acc = fmaf(st[r], cc[r], acc);
             }
+            acc = group_sum(acc, RG);
+            if (rgi == 0) sO[tt * CB + cl] = acc + dskip * xp;
         }
         __syncthreads();
-        for (int i = tid; i < nt * P; i += blockDim.x) {
-            const int tt = i / P, q = i - tt * P;
-            out[(size_t)(tile + tt) * H * P + (size_t)h * P + q] = sum_groups(part + (size_t)tt * RG * P, RG, P, q) + dskip * sX[tt * P + q];
+        for (int i = tid; i < nt * CB; i += blockDim.x) {
+            const int tt = i / CB, q = i - tt * CB;
+            if (p0 + q < P) out[(size_t)(tile + tt) * H * P + (size_t)h * P + p0 + q] = sO[tt * CB + q];
         }
     }
     if (active) {
 #pragma unroll
         for (int r = 0; r < RPT; r++) {
-            const int n = rg * RPT + r;
+            const int n = rgi * RPT + r;
             if (n < N) S[(size_t)n * P + p] = st[r];
         }
     }
@@ -202,117 +207,115 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
 // h at v_off + h * dv.  beta_raw [T, ld_b] of type TD, head h at column beta_off + h.  a_raw [T, ld_a] float32, head
 // h's d channels at a_off + h * d; dt_bias [H * d].
 template <typename TD, int RPT>
-__global__ void __launch_bounds__(RPT == 16 ? 1024 : RPT == 128 ? 256 : 512)
-delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, int v_off,
-                                  const TD* __restrict__ beta_raw, int ld_b, int beta_off, const float* __restrict__ a_raw, int ld_a,
-                                  int a_off, const void* __restrict__ dt_bias, const void* __restrict__ a_log, int w_dt,
-                                  float* __restrict__ state, size_t state_ld, float* __restrict__ out, GfbBatch b, int H, int KH,
-                                  int d, int dv, float q_scale, float unit_eps) {
+__global__ void __launch_bounds__(32 * SCAN_WARPS)
+delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, int v_off, const TD* __restrict__ beta_raw, int ld_b,
+                  int beta_off, const float* __restrict__ a_raw, int ld_a, int a_off, const void* __restrict__ dt_bias,
+                  const void* __restrict__ a_log, int w_dt, float* __restrict__ state, size_t state_ld, float* __restrict__ out,
+                  GfbBatch b, int H, int KH, int d, int dv, float q_scale, float unit_eps, int RG) {
     extern __shared__ float sm[];
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int s = blockIdx.x, h = blockIdx.y, kh = h / (H / KH);
-    const int RG = (d + RPT - 1) / RPT;
-    float* sQ = sm;                       // [TB][d]
-    float* sK = sQ + TB * d;              // [TB][d]
-    float* sG = sK + TB * d;              // [TB][d]
-    float* sV = sG + TB * d;              // [TB][dv]
-    float* sBeta = sV + TB * dv;          // [TB]
-    float* part1 = sBeta + TB;            // [2][RG][dv]
-    float* part2 = part1 + 2 * RG * dv;   // [TB][RG][dv]
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
-    const bool active = tid < dv * RG;
-    const int p = active ? tid % dv : 0, rg = active ? tid / dv : 0;
+    const int CW = 32 / RG, CB = SCAN_WARPS * CW, NP = RG * (RPT + 1);
+    float* sQ = sm;                       // [TB][NP]
+    float* sK = sQ + TB * NP;             // [TB][NP]
+    float* sG = sK + TB * NP;             // [TB][NP]
+    float* sV = sG + TB * NP;             // [TB][CB]
+    float* sO = sV + TB * CB;             // [TB][CB]
+    float* sBeta = sO + TB * CB;          // [TB]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rgi = lane % RG, cl = warp * CW + lane / RG;
+    const int p0 = blockIdx.z * CB, p = p0 + cl;
+    const bool active = p < dv;
     const int t0 = b.cu_seqlens[s], t1 = b.cu_seqlens[s + 1];
     float* S = state + (size_t)b.slots[s] * state_ld + (size_t)h * d * dv;
     float st[RPT];
 #pragma unroll
     for (int r = 0; r < RPT; r++) {
-        const int i = rg * RPT + r;
+        const int i = rgi * RPT + r;
         st[r] = (active && i < d) ? S[(size_t)i * dv + p] : 0.f;
     }
     const float rate = expf(ldw(a_log, w_dt, h));
     for (int tile = t0; tile < t1; tile += TB) {
         const int nt = min(TB, t1 - tile);
         __syncthreads();
-        for (int i = tid; i < nt * d; i += blockDim.x) {
-            const int tt = i / d, c = i - tt * d;
-            const float* row = qkv + (size_t)(tile + tt) * ldq;
-            sQ[tt * d + c] = row[q_off + kh * d + c];
-            sK[tt * d + c] = row[k_off + kh * d + c];
-            const float a = a_raw[(size_t)(tile + tt) * ld_a + a_off + (size_t)h * d + c] + ldw(dt_bias, w_dt, (size_t)h * d + c);
-            sG[tt * d + c] = expf(-rate * softplus_f(a));
+        for (int i = tid; i < nt * RG * RPT; i += blockDim.x) {
+            const int tt = i / (RG * RPT), c = i - tt * RG * RPT;
+            const int at = tt * NP + padded(c, RPT);
+            if (c < d) {
+                const float* row = qkv + (size_t)(tile + tt) * ldq;
+                sQ[at] = row[q_off + kh * d + c];
+                sK[at] = row[k_off + kh * d + c];
+                const float a = a_raw[(size_t)(tile + tt) * ld_a + a_off + (size_t)h * d + c] + ldw(dt_bias, w_dt, (size_t)h * d + c);
+                sG[at] = expf(-rate * softplus_f(a));
+            } else {
+                sQ[at] = 0.f; sK[at] = 0.f; sG[at] = 1.f;
+            }
         }
-        for (int i = tid; i < nt * dv; i += blockDim.x) {
-            const int tt = i / dv, c = i - tt * dv;
-            sV[tt * dv + c] = qkv[(size_t)(tile + tt) * ldq + v_off + (size_t)h * dv + c];
+        for (int i = tid; i < nt * CB; i += blockDim.x) {
+            const int tt = i / CB, c = i - tt * CB;
+            sV[tt * CB + c] = p0 + c < dv ? qkv[(size_t)(tile + tt) * ldq + v_off + (size_t)h * dv + p0 + c] : 0.f;
         }
         if (tid < nt) sBeta[tid] = sigmoid_f(gfb_to_f32(beta_raw[(size_t)(tile + tid) * ld_b + beta_off + h]));
         __syncthreads();
         // unit vectors: a warp per (token, q or k); lanes add strided squares, a fixed tree adds the lanes
-        for (int item = warp; item < 2 * nt; item += nwarp) {
-            float* vec = (item & 1 ? sK : sQ) + (item >> 1) * d;
+        for (int item = warp; item < 2 * nt; item += SCAN_WARPS) {
+            float* vec = (item & 1 ? sK : sQ) + (item >> 1) * NP;
             float ss = 0.f;
-            for (int c = lane; c < d; c += 32) ss = fmaf(vec[c], vec[c], ss);
+            for (int c = lane; c < d; c += 32) { const float v = vec[padded(c, RPT)]; ss = fmaf(v, v, ss); }
             ss = gfb_warp_sum(ss);
             const float f = (1.0f / sqrtf(ss + unit_eps)) * (item & 1 ? 1.0f : q_scale);
-            for (int c = lane; c < d; c += 32) vec[c] *= f;
+            for (int c = lane; c < d; c += 32) vec[padded(c, RPT)] *= f;
         }
         __syncthreads();
         for (int tt = 0; tt < nt; tt++) {
-            float* p1 = part1 + (size_t)(tt & 1) * RG * dv;
+            const float* gg = sG + tt * NP + rgi * (RPT + 1);
+            const float* kk = sK + tt * NP + rgi * (RPT + 1);
+            const float* qq = sQ + tt * NP + rgi * (RPT + 1);
+            float kr[RPT];
             float acc = 0.f;
-            if (active) {
 #pragma unroll
-                for (int r = 0; r < RPT; r++) {
-                    const int i = rg * RPT + r;
-                    if (i < d) {
-                        st[r] *= sG[tt * d + i];
-                        acc = fmaf(st[r], sK[tt * d + i], acc);
-                    }
-                }
-                if (RG > 1) p1[(size_t)rg * dv + p] = acc;
+            for (int r = 0; r < RPT; r++) {
+                kr[r] = kk[r];
+                st[r] *= gg[r];
+                acc = fmaf(st[r], kr[r], acc);
             }
-            if (RG > 1) {
-                __syncthreads();
-                if (active) acc = sum_groups(p1, RG, dv, p);
-            }
-            if (active) {
-                const float u = sBeta[tt] * (sV[tt * dv + p] - acc);
-                float o = 0.f;
+            acc = group_sum(acc, RG);
+            const float u = sBeta[tt] * (sV[tt * CB + cl] - acc);
+            float o = 0.f;
 #pragma unroll
-                for (int r = 0; r < RPT; r++) {
-                    const int i = rg * RPT + r;
-                    if (i < d) {
-                        st[r] = fmaf(sK[tt * d + i], u, st[r]);
-                        o = fmaf(st[r], sQ[tt * d + i], o);
-                    }
-                }
-                part2[((size_t)tt * RG + rg) * dv + p] = o;
+            for (int r = 0; r < RPT; r++) {
+                st[r] = fmaf(kr[r], u, st[r]);
+                o = fmaf(st[r], qq[r], o);
             }
+            o = group_sum(o, RG);
+            if (rgi == 0) sO[tt * CB + cl] = o;
         }
         __syncthreads();
-        for (int i = tid; i < nt * dv; i += blockDim.x) {
-            const int tt = i / dv, c = i - tt * dv;
-            out[(size_t)(tile + tt) * H * dv + (size_t)h * dv + c] = sum_groups(part2 + (size_t)tt * RG * dv, RG, dv, c);
+        for (int i = tid; i < nt * CB; i += blockDim.x) {
+            const int tt = i / CB, c = i - tt * CB;
+            if (p0 + c < dv) out[(size_t)(tile + tt) * H * dv + (size_t)h * dv + p0 + c] = sO[tt * CB + c];
         }
     }
     if (active) {
 #pragma unroll
         for (int r = 0; r < RPT; r++) {
-            const int i = rg * RPT + r;
+            const int i = rgi * RPT + r;
             if (i < d) S[(size_t)i * dv + p] = st[r];
         }
     }
 }
 
-// rows per thread for a state of `rows` x `cols`: the fewest whose block fits its thread limit; 0 if none does
-static int pick_rpt(int rows, int cols, int* threads) {
-    const int rpt[4] = {16, 32, 64, 128}, limit[4] = {1024, 512, 512, 256};
-    for (int i = 0; i < 4; i++) {
-        const int need = cols * ((rows + rpt[i] - 1) / rpt[i]);
-        if (need <= limit[i]) {
-            *threads = (need + 31) / 32 * 32;
+// rows per lane and lanes per column for a state of `rows` rows: the fewest rows per lane that need at most 32 lanes;
+// 0 if none does
+static int pick_rpt(int rows, int* rg) {
+    const int rpt[3] = {16, 32, 64};
+    for (int i = 0; i < 3; i++) {
+        const int need = (rows + rpt[i] - 1) / rpt[i];
+        if (need <= 32) {
+            int g = 1;
+            while (g < need) g <<= 1;
+            *rg = g;
             return rpt[i];
         }
     }
@@ -337,21 +340,22 @@ GFB_API int gfb_ssd_scan(const float* x, int ldx, int b_off, int c_off, const vo
                          int n_seqs, int n_tokens, int H, int P, int N, int G, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (G <= 0 || H % G) return gfb_fail("gfb_ssd_scan: %d heads do not divide into %d groups", H, G);
-    if (H > 65535) return gfb_fail("gfb_ssd_scan: %d heads exceed the grid limit", H);
-    int threads = 0;
-    const int rpt = pick_rpt(N, P, &threads);
-    if (!rpt) return gfb_fail("gfb_ssd_scan: a state of %d x %d per head does not fit a block", N, P);
-    const int RG = (N + rpt - 1) / rpt;
-    const size_t smem = ((size_t)TB * (2 * N + P + 2) + (size_t)TB * RG * P) * sizeof(float);
+    int RG = 0;
+    const int rpt = pick_rpt(N, &RG);
+    if (!rpt) return gfb_fail("gfb_ssd_scan: a state of %d rows per head does not fit a warp", N);
+    const int CB = SCAN_WARPS * (32 / RG);
+    const unsigned slices = (unsigned)((P + CB - 1) / CB);
+    if (H > 65535 || slices > 65535) return gfb_fail("gfb_ssd_scan: %d heads of %d columns exceed the grid limit", H, P);
+    const size_t smem = ((size_t)TB * (2 * RG * (rpt + 1) + 2 * CB + 2)) * sizeof(float);
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     cudaError_t e = cudaSuccess;
 #define GO(TD, R)                                                                                                          \
     do {                                                                                                                   \
         if (allow_smem(ssd_scan_kernel<TD, R>, smem, "gfb_ssd_scan")) return 1;                                            \
-        e = gfb_launch(ssd_scan_kernel<TD, R>, dim3(n_seqs, H), dim3(threads), smem, stream, x, ldx, b_off, c_off, (const TD*)dt_raw, \
-                       ld_dt, dt_off, dt_bias, a_log, skip, w_dt, state, (size_t)state_ld, out, b, H, P, N, G);            \
+        e = gfb_launch(ssd_scan_kernel<TD, R>, dim3(n_seqs, H, slices), dim3(32 * SCAN_WARPS), smem, stream, x, ldx, b_off, c_off, \
+                       (const TD*)dt_raw, ld_dt, dt_off, dt_bias, a_log, skip, w_dt, state, (size_t)state_ld, out, b, H, P, N, G, RG); \
     } while (0)
-#define PICK(TD) do { if (rpt == 16) GO(TD, 16); else if (rpt == 32) GO(TD, 32); else if (rpt == 64) GO(TD, 64); else GO(TD, 128); } while (0)
+#define PICK(TD) do { if (rpt == 16) GO(TD, 16); else if (rpt == 32) GO(TD, 32); else GO(TD, 64); } while (0)
     if (dt_dt == GFB_BF16) PICK(__nv_bfloat16);
     else if (dt_dt == GFB_F32) PICK(float);
     else return gfb_fail("gfb_ssd_scan: unknown type %d", dt_dt);
@@ -368,22 +372,23 @@ GFB_API int gfb_delta_rule(const float* qkv, int ldq, int q_off, int k_off, int 
                            float unit_eps, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (KH <= 0 || H % KH) return gfb_fail("gfb_delta_rule: %d heads do not divide into %d query/key heads", H, KH);
-    if (H > 65535) return gfb_fail("gfb_delta_rule: %d heads exceed the grid limit", H);
-    int threads = 0;
-    const int rpt = pick_rpt(d, dv, &threads);
-    if (!rpt) return gfb_fail("gfb_delta_rule: a state of %d x %d per head does not fit a block", d, dv);
-    const int RG = (d + rpt - 1) / rpt;
-    const size_t smem = ((size_t)TB * (3 * d + dv + 1) + (size_t)(2 + TB) * RG * dv) * sizeof(float);
+    int RG = 0;
+    const int rpt = pick_rpt(d, &RG);
+    if (!rpt) return gfb_fail("gfb_delta_rule: a state of %d rows per head does not fit a warp", d);
+    const int CB = SCAN_WARPS * (32 / RG);
+    const unsigned slices = (unsigned)((dv + CB - 1) / CB);
+    if (H > 65535 || slices > 65535) return gfb_fail("gfb_delta_rule: %d heads of %d columns exceed the grid limit", H, dv);
+    const size_t smem = ((size_t)TB * (3 * RG * (rpt + 1) + 2 * CB + 1)) * sizeof(float);
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     cudaError_t e = cudaSuccess;
 #define GO(TD, R)                                                                                                          \
     do {                                                                                                                   \
         if (allow_smem(delta_rule_kernel<TD, R>, smem, "gfb_delta_rule")) return 1;                                        \
-        e = gfb_launch(delta_rule_kernel<TD, R>, dim3(n_seqs, H), dim3(threads), smem, stream, qkv, ldq, q_off, k_off, v_off,   \
-                       (const TD*)beta_raw, ld_b, beta_off, a_raw, ld_a, a_off, dt_bias, a_log, w_dt, state, (size_t)state_ld, \
-                       out, b, H, KH, d, dv, q_scale, unit_eps);                                                           \
+        e = gfb_launch(delta_rule_kernel<TD, R>, dim3(n_seqs, H, slices), dim3(32 * SCAN_WARPS), smem, stream, qkv, ldq, q_off, k_off, \
+                       v_off, (const TD*)beta_raw, ld_b, beta_off, a_raw, ld_a, a_off, dt_bias, a_log, w_dt, state,        \
+                       (size_t)state_ld, out, b, H, KH, d, dv, q_scale, unit_eps, RG);                                     \
     } while (0)
-#define PICK(TD) do { if (rpt == 16) GO(TD, 16); else if (rpt == 32) GO(TD, 32); else if (rpt == 64) GO(TD, 64); else GO(TD, 128); } while (0)
+#define PICK(TD) do { if (rpt == 16) GO(TD, 16); else if (rpt == 32) GO(TD, 32); else GO(TD, 64); } while (0)
     if (b_dt == GFB_BF16) PICK(__nv_bfloat16);
     else if (b_dt == GFB_F32) PICK(float);
     else return gfb_fail("gfb_delta_rule: unknown type %d", b_dt);
@@ -393,30 +398,32 @@ GFB_API int gfb_delta_rule(const float* qkv, int ldq, int q_off, int k_off, int 
 }
 
 // ------------------------------------------------------------------------------ gated group norm ----
-// One warp per (token, group of `gs` columns): v = y, times act(gate) first if gate_first; n = v / sqrt(mean(v^2) + eps)
-// * weight[col % w_len]; times act(gate) behind the norm otherwise.  act: 0 = SiLU, 1 = sigmoid.
-template <typename TG, typename TO>
+// One warp per (token, group of `gs` columns), or one block for a large group (BLOCK): v = y, times act(gate) first if
+// gate_first; n = v / sqrt(mean(v^2) + eps) * weight[col % w_len]; times act(gate) behind the norm otherwise.
+// act: 0 = SiLU, 1 = sigmoid.
+template <typename TG, typename TO, bool BLOCK>
 __global__ void gated_norm_kernel(const float* __restrict__ y, const TG* __restrict__ gate, int ld_gate, int gate_off,
                                   const void* __restrict__ weight, int w_dt, int w_len, TO* __restrict__ out, int T, int groups,
                                   int gs, float eps, int act, int gate_first) {
+    __shared__ float scratch[32];
     gfb_pdl_launch();
     gfb_pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = BLOCK ? threadIdx.x : (threadIdx.x & 31), step = BLOCK ? blockDim.x : 32;
+    const long item = BLOCK ? (long)blockIdx.x : (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= (long)T * groups) return;
     const int t = (int)(item / groups), g = (int)(item - (long)t * groups);
     const float* yr = y + ((size_t)t * groups + g) * gs;
     const TG* gr = gate + (size_t)t * ld_gate + gate_off + (size_t)g * gs;
     float ss = 0.f;
-    for (int c = lane; c < gs; c += 32) {
+    for (int c = lane; c < gs; c += step) {
         float v = yr[c];
         if (gate_first) { const float z = gfb_to_f32(gr[c]); v *= act ? sigmoid_f(z) : silu_f(z); }
         ss = fmaf(v, v, ss);
     }
-    ss = gfb_warp_sum(ss);
+    ss = BLOCK ? gfb_block_sum(ss, scratch) : gfb_warp_sum(ss);
     const float r = 1.0f / sqrtf(ss / (float)gs + eps);
     TO* o = out + ((size_t)t * groups + g) * gs;
-    for (int c = lane; c < gs; c += 32) {
+    for (int c = lane; c < gs; c += step) {
         float v = yr[c];
         const float z = gfb_to_f32(gr[c]);
         const float a = act ? sigmoid_f(z) : silu_f(z);
@@ -435,11 +442,18 @@ GFB_API int gfb_gated_norm(const float* y, const void* gate, int gate_dt, int ld
     if (T <= 0 || groups <= 0 || gs <= 0) return 0;
     if (w_len <= 0) return gfb_fail("gfb_gated_norm: a weight of %d numbers", w_len);
     const long items = (long)T * groups;
-    const unsigned blocks = (unsigned)((items + 3) / 4);
+    const bool big = gs > 512;                                  // a block per group instead of a warp
+    const unsigned blocks = big ? (unsigned)items : (unsigned)((items + 3) / 4);
+    const unsigned threads = big ? 256 : 128;
     typedef __nv_bfloat16 bf16;
     cudaError_t e;
-#define GO(TG, TO) e = gfb_launch(gated_norm_kernel<TG, TO>, dim3(blocks), dim3(128), 0, stream, y, (const TG*)gate, ld_gate, gate_off, \
-                                  weight, w_dt, w_len, (TO*)out, T, groups, gs, eps, act, gate_first)
+#define GO(TG, TO)                                                                                                                \
+    do {                                                                                                                          \
+        if (big) e = gfb_launch(gated_norm_kernel<TG, TO, true>, dim3(blocks), dim3(threads), 0, stream, y, (const TG*)gate, ld_gate, \
+                                gate_off, weight, w_dt, w_len, (TO*)out, T, groups, gs, eps, act, gate_first);                    \
+        else e = gfb_launch(gated_norm_kernel<TG, TO, false>, dim3(blocks), dim3(threads), 0, stream, y, (const TG*)gate, ld_gate,    \
+                            gate_off, weight, w_dt, w_len, (TO*)out, T, groups, gs, eps, act, gate_first);                        \
+    } while (0)
     if (gate_dt == GFB_BF16 && out_dt == GFB_BF16) GO(bf16, bf16);
     else if (gate_dt == GFB_F32 && out_dt == GFB_BF16) GO(float, bf16);
     else if (gate_dt == GFB_F32 && out_dt == GFB_F32) GO(float, float);

@@ -145,12 +145,11 @@ def latent_prepare(src, q_off: int, kv_off: int, q_out, kv: PagedKV, batch: Batc
 
 
 def headwise_linear(a, w, out, n_head: int, k: int, n: int, a_off: int = 0, a_stride: Optional[int] = None, out_off: int = 0,
-                    out_stride: Optional[int] = None, layout: str = "kn", gate=None, gate_off: int = 0):
-    """A product with a weight per head: out[t, h, :] = W_h applied to a[t, h, :].  a [T, Wa]: head h's k inputs start
-    at column a_off + h * a_stride; out [T, Wo]: its n outputs at out_off + h * out_stride; w [n_head, k, n]
-    (layout 'kn': out = a W_h) or [n_head, n, k] ('nk': out = W_h a).  gate [T, Wg] (or None): the result is
-    multiplied by sigmoid(gate[t, gate_off + h * n + j])."""
-    return kernels().headwise_linear(a, w, out, n_head, k, n, a_off, a_stride, out_off, out_stride, layout, gate, gate_off)
+                    out_stride: Optional[int] = None, gate=None, gate_off: int = 0):
+    """A product with a weight per head: out[t, h, :] = a[t, h, :] W_h.  a [T, Wa]: head h's k inputs start at column
+    a_off + h * a_stride; out [T, Wo]: its n outputs at out_off + h * out_stride; w [n_head, k, n].  gate [T, Wg] (or
+    None): the result is multiplied by sigmoid(gate[t, gate_off + h * n + j])."""
+    return kernels().headwise_linear(a, w, out, n_head, k, n, a_off, a_stride, out_off, out_stride, gate, gate_off)
 
 
 def short_conv(src, col_off: int, channels: int, weight, bias, state, state_off: int, out, batch: BatchMeta, act: bool = True):

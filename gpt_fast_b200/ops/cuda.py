@@ -304,8 +304,7 @@ class CudaKernels:
                    c_float(eps), c_int(n_head), c_int(head_dim), c_int(rot_dim), c_int(rank), c_int(_PAIRING[pairing]),
                    c_int(1 if append else 0), _ptr(batch.status), _stream())
 
-    def headwise_linear(self, a, w, out, n_head, k, n, a_off=0, a_stride=None, out_off=0, out_stride=None, layout="kn",
-                        gate=None, gate_off=0):
+    def headwise_linear(self, a, w, out, n_head, k, n, a_off=0, a_stride=None, out_off=0, out_stride=None, gate=None, gate_off=0):
         T = a.shape[0]
         a_stride = k if a_stride is None else a_stride
         out_stride = n if out_stride is None else out_stride
@@ -313,15 +312,14 @@ class CudaKernels:
         _need(out, a.dtype, name="head-wise output")
         if a.dim() != 2 or out.dim() != 2 or out.shape[0] != T:
             _fail("head-wise product: input and output are [tokens, columns]")
-        _need(w, a.dtype, (n_head, k, n) if layout == "kn" else (n_head, n, k), "head-wise weight")
+        _need(w, a.dtype, (n_head, k, n), "head-wise weight")
         if a_off + (n_head - 1) * a_stride + k > a.shape[1] or out_off + (n_head - 1) * out_stride + n > out.shape[1]:
             _fail("head-wise product: the heads do not fit the rows")
         if gate is not None:
             _need(gate, a.dtype, name="gate")
             if gate.shape[0] != T or gate_off + n_head * n > gate.shape[1]:
                 _fail("head-wise product: the gate does not fit")
-        self._call("latent", "gfb_headwise_linear", _ptr(a), c_int(_dt(a)), c_int(a.shape[1]), c_int(a_off), c_int(a_stride), _ptr(w),
-                   c_int(1 if layout == "kn" else 0), _ptr(out), c_int(out.shape[1]), c_int(out_off), c_int(out_stride), _ptr(gate),
+        self._call("latent", "gfb_headwise_linear", _ptr(a), c_int(_dt(a)), c_int(a.shape[1]), c_int(a_off), c_int(a_stride), _ptr(w), _ptr(out), c_int(out.shape[1]), c_int(out_off), c_int(out_stride), _ptr(gate),
                    c_int(gate.shape[1] if gate is not None else 0), c_int(gate_off), c_int(T), c_int(n_head), c_int(k), c_int(n),
                    _stream())
 
@@ -577,6 +575,15 @@ class CudaKernels:
         if sink is not None:
             _need(sink, torch.float32, (n_head,), "sink")
         plain = chunk is None and sink is None
+        if (values_in_keys and q.dtype == torch.bfloat16 and n_kv == 1 and chunk is None and sink is None
+                and not window and head_dim % 16 == 0 and dv % 16 == 0 and dv <= 512 and dv < head_dim and kv.page_size % 32 == 0
+                and (64 + 2 * 32) * (head_dim + 8) * 2 <= 220 * 1024):
+            # a latent that all heads share: the tensor-core kernel that fetches every cached row once per 64 (token, head)
+            # pairs of a sequence (a decode step's heads are the rows of one MMA)
+            return self._call("latent", "gfb_latent_attention", _ptr(q), _ptr(out), _ptr(kv.k_pool), _ptr(kv.page_table),
+                              c_int(kv.page_table.shape[1]), c_int(kv.page_size), c_int(kv.k_pool.shape[0]), *self._batch_args(batch),
+                              c_int(int(batch.max_q_len)), c_int(n_head), c_int(head_dim), c_int(dv), c_float(scale), _ptr(batch.status),
+                              _stream())
         if (not values_in_keys and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
                 and (head_dim in (64, 128) or (plain and head_dim % 8 == 0 and head_dim <= 256))):
             # the tensor-core kernels; a block mask or a sink only at the head sizes they are built for

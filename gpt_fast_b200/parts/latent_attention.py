@@ -42,13 +42,13 @@ class LatentAttention:
         # rows of the fused projection: queries, down projection, gate
         self.w_in = torch.cat([tensors["wq"], tensors["wdkv"], tensors["wg"]]).contiguous()
         self.wuk = tensors["wuk"].view(self.n_head, self.head_dim, self.rank)         # [H][k = head_dim][n = rank]
-        self.wuv = tensors["wuv"].view(self.n_head, self.v_head_dim, self.rank)       # [H][n = v_head_dim][k = rank]
+        self.wuv = tensors["wuv"].view(self.n_head, self.v_head_dim, self.rank).transpose(1, 2).contiguous()   # [H][k = rank][n = v_head_dim]
         self.wo, self.latent_norm = tensors["wo"], tensors["latent_norm"]
 
     def export(self):
         H, d, r, dv, R = self.n_head, self.head_dim, self.rot_dim, self.v_head_dim, self.rank
         wq, wdkv, wg = self.w_in.split([H * (d + r), R + r, H * dv])
-        return {"wq": wq, "wdkv": wdkv, "wg": wg, "wuk": self.wuk.reshape(H * d, R), "wuv": self.wuv.reshape(H * dv, R),
+        return {"wq": wq, "wdkv": wdkv, "wg": wg, "wuk": self.wuk.reshape(H * d, R), "wuv": self.wuv.transpose(1, 2).reshape(H * dv, R),
                 "wo": self.wo, "latent_norm": self.latent_norm}
 
     def cache_needs(self) -> CacheNeeds:
@@ -64,10 +64,9 @@ class LatentAttention:
         q = torch.empty(T, H, R + r, dtype=self.dtype, device=h.device)
         ops.latent_prepare(proj, q_off, kv_off, q, view.kv, batch, H, d, r, R, self.latent_norm, self.eps,
                            self.position.table, self.position.pairing, append)
-        ops.headwise_linear(proj, self.wuk, q.view(T, H * (R + r)), H, d, R, a_off=q_off, a_stride=d + r, out_stride=R + r,
-                            layout="kn")
+        ops.headwise_linear(proj, self.wuk, q.view(T, H * (R + r)), H, d, R, a_off=q_off, a_stride=d + r, out_stride=R + r)
         o = torch.empty(T, H * R, dtype=self.dtype, device=h.device)
         ops.attention(q, view.kv, batch, o, H, 1, R + r, self.scale, self.window, v_head_dim=R, values_in_keys=True)
         y = torch.empty(T, H * dv, dtype=self.dtype, device=h.device)
-        ops.headwise_linear(o, self.wuv, y, H, R, dv, layout="nk", gate=proj, gate_off=g_off)
+        ops.headwise_linear(o, self.wuv, y, H, R, dv, gate=proj, gate_off=g_off)
         as_residual(residual).add_linear(y, self.wo)

@@ -131,13 +131,12 @@ class PlainOps:
                 raise IndexError("token lands on a page the slot does not hold")
             kv.k_pool[page, 0, pos % kv.page_size] = torch.cat([c, kr], -1).to(kv.k_pool.dtype)
 
-    def headwise_linear(self, a, w, out, n_head, k, n, a_off=0, a_stride=None, out_off=0, out_stride=None, layout="kn",
-                        gate=None, gate_off=0):
+    def headwise_linear(self, a, w, out, n_head, k, n, a_off=0, a_stride=None, out_off=0, out_stride=None, gate=None, gate_off=0):
         a_stride = k if a_stride is None else a_stride
         out_stride = n if out_stride is None else out_stride
         for h in range(n_head):
             x = a[:, a_off + h * a_stride:a_off + h * a_stride + k].double()
-            y = x @ (w[h].double() if layout == "kn" else w[h].double().T)
+            y = x @ w[h].double()
             if gate is not None:
                 y = y * torch.sigmoid(gate[:, gate_off + h * n:gate_off + (h + 1) * n].double())
             out[:, out_off + h * out_stride:out_off + h * out_stride + n] = y.to(out.dtype)

@@ -140,21 +140,21 @@ def test_latent_prepare_and_headwise(dtype, H, d, r, R, pairing):
     ops.latent_prepare(src, q_off, kv_off, q, kv, batch, H, d, r, R, nw, 1e-5, rope.table, pairing)
     ops.check_status(batch.status)
     wuk = rnd(H, d, R, dtype=dtype, scale=0.3, seed=5)
-    ops.headwise_linear(src, wuk, q.view(T, -1), H, d, R, a_off=q_off, a_stride=d + r, out_stride=R + r, layout="kn")
+    ops.headwise_linear(src, wuk, q.view(T, -1), H, d, R, a_off=q_off, a_stride=d + r, out_stride=R + r)
     kv2 = PagedKV(torch.zeros_like(kv.k_pool).cpu(), kv.v_pool.cpu(), table.cpu(), 64)
     q2 = torch.zeros(T, H, R + r, dtype=dtype)
     REF.latent_prepare(src.cpu(), q_off, kv_off, q2, kv2, cpu_batch(batch), H, d, r, R, nw.cpu(), 1e-5, rope.table.cpu(), pairing)
-    REF.headwise_linear(src.cpu(), wuk.cpu(), q2.view(T, -1), H, d, R, a_off=q_off, a_stride=d + r, out_stride=R + r, layout="kn")
+    REF.headwise_linear(src.cpu(), wuk.cpu(), q2.view(T, -1), H, d, R, a_off=q_off, a_stride=d + r, out_stride=R + r)
     t = tol(dtype)
     torch.testing.assert_close(d64(q), d64(q2), **t)
     torch.testing.assert_close(d64(kv.k_pool), d64(kv2.k_pool), **t)
-    # the other layout, with a sigmoid gate
+    # many inputs per head, few outputs, with a sigmoid gate
     o = rnd(T, H * R, dtype=dtype, seed=6)
-    wuv = rnd(H, 7, R, dtype=dtype, scale=0.3, seed=7)
+    wuv = rnd(H, R, 7, dtype=dtype, scale=0.3, seed=7)
     gate = rnd(T, H * 7 + 4, dtype=dtype, seed=8)
     y, y2 = torch.empty(T, H * 7, dtype=dtype, device=DEV), torch.empty(T, H * 7, dtype=dtype)
-    ops.headwise_linear(o, wuv, y, H, R, 7, layout="nk", gate=gate, gate_off=4)
-    REF.headwise_linear(o.cpu(), wuv.cpu(), y2, H, R, 7, layout="nk", gate=gate.cpu(), gate_off=4)
+    ops.headwise_linear(o, wuv, y, H, R, 7, gate=gate, gate_off=4)
+    REF.headwise_linear(o.cpu(), wuv.cpu(), y2, H, R, 7, gate=gate.cpu(), gate_off=4)
     torch.testing.assert_close(d64(y), d64(y2), **t)
 
 
@@ -310,3 +310,43 @@ def test_gated_norm(dtype, groups, gs, shared, act, first):
     v = d64(y) * a if first else d64(y)
     n = pg.rms(v.view(T, groups, gs), 1e-5).reshape(T, C) * d64(w).repeat(C // w.numel())
     torch.testing.assert_close(d64(out), n if first else n * a, **tol(dtype))
+
+
+# ---- attention on the latent with many queries: the tensor-core kernel -----------------------------------------------------
+
+@pytest.mark.parametrize("H,R,r", [(16, 64, 16), (3, 48, 16), (5, 512, 64), (1, 16, 16), (8, 128, 32)])
+def test_latent_attention_many_queries(H, R, r):
+    """Portions that start at 0, in the middle of a tile of 32 keys, at a page's edge and far into a sequence; heads
+    that do not fill the 16 rows of an MMA; every row masked by its own position."""
+    dtype = torch.bfloat16
+    q_lens, starts = [70, 33, 2, 5], [0, 61, 31, 640]
+    _latent_attention_case(H, R, r, q_lens, starts)
+
+
+@pytest.mark.parametrize("H,R,r", [(16, 64, 16), (3, 48, 16), (40, 32, 16)])
+def test_latent_attention_decode_step(H, R, r):
+    """One query per sequence: a sequence's heads are the rows of the MMA (40 heads: three row tiles, the last part-filled)."""
+    _latent_attention_case(H, R, r, [1, 1, 1, 1], [0, 31, 64, 644], marked=((0, 7), (0, 643)))
+
+
+def _latent_attention_case(H, R, r, q_lens, starts, marked=((1, 7), (4, 643))):
+    dtype = torch.bfloat16
+    batch, table, n_pages = make_batch(q_lens, starts, 6, 64, 12, seed=3)
+    kv = PagedKV(rnd(n_pages, 1, 64, R + r, dtype=dtype, scale=0.5, seed=1), torch.zeros(n_pages, 1, 64, 0, dtype=dtype, device=DEV), table, 64)
+    q = rnd(batch.n_tokens, H, R + r, dtype=dtype, scale=0.5, seed=2)
+    # the last sequence's second query looks for a key far back, its last query for the key just before it
+    slot, t0 = int(batch.slots[3]), int(batch.cu_seqlens[3])
+    for which, key in marked[-1:] if marked[0][0] == marked[1][0] else marked:
+        kv.k_pool[int(table[slot, key // 64]), 0, key % 64] = (q[t0 + which, H - 1] * 30).to(dtype)
+    out = torch.empty(batch.n_tokens, H * R, dtype=dtype, device=DEV)
+    with ops.trace() as rec:
+        ops.attention(q, kv, batch, out, H, 1, R + r, 0.3, v_head_dim=R, values_in_keys=True)
+    assert [label for label, _, _ in rec] == ["gfb_latent_attention"]
+    ops.check_status(batch.status)
+    out2 = torch.empty(batch.n_tokens, H * R, dtype=dtype)
+    REF.attention(q.cpu(), PagedKV(kv.k_pool.cpu(), kv.v_pool.cpu(), table.cpu(), 64), cpu_batch(batch), out2, H, 1, R + r, 0.3,
+                  v_head_dim=R, values_in_keys=True)
+    torch.testing.assert_close(d64(out), d64(out2), rtol=3e-2, atol=3e-2)
+    for which, key in marked[-1:] if marked[0][0] == marked[1][0] else marked:
+        row = kv.k_pool[int(table[slot, key // 64]), 0, key % 64, :R]
+        torch.testing.assert_close(d64(out[t0 + which, (H - 1) * R:]), d64(row), rtol=0.05, atol=0.05)

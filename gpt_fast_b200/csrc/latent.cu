@@ -110,6 +110,90 @@ GFB_API int gfb_latent_prepare(const void* src, int dt, int ld, int q_off, int k
     return gfb_check(e, "gfb_latent_prepare");
 }
 
+// ---------------------------------------------------------------- a product with a weight per head, on tensor cores -----
+// out[t, h, n] = sum_k in[t, h, k] * W_h[k, n] (see below) for bfloat16 with 16-byte aligned rows, `mma.sync.m16n8k16`: a block takes 64 tokens (four warps of 16 rows) of one head and 64 output columns and
+// walks over k in pieces of 64; the weight piece [k][n] is the B operand, transposed on its way into the registers.
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+constexpr int HT_ROWS = 64, HT_COLS = 64, HT_K = 64, HT_PAD = 8;
+
+__global__ void __launch_bounds__(128)
+headwise_linear_tc_kernel(const __nv_bfloat16* __restrict__ in, int ld_in, int in_off, int in_stride, const __nv_bfloat16* __restrict__ w,
+                          __nv_bfloat16* __restrict__ out, int ld_out, int out_off, int out_stride, const __nv_bfloat16* __restrict__ gate,
+                          int ld_gate, int gate_off, int n_tokens, int K, int N) {
+    __shared__ __align__(16) __nv_bfloat16 sA[HT_ROWS][HT_K + HT_PAD];
+    __shared__ __align__(16) __nv_bfloat16 sW[HT_K][HT_COLS + HT_PAD];
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int h = blockIdx.y, t0 = blockIdx.x * HT_ROWS, n0 = blockIdx.z * HT_COLS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const __nv_bfloat16* a_base = in + in_off + (size_t)h * in_stride;
+    const __nv_bfloat16* w_base = w + (size_t)h * K * N;
+    float acc[HT_COLS / 8][4];
+#pragma unroll
+    for (int j = 0; j < HT_COLS / 8; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += HT_K) {
+        __syncthreads();
+        for (int c = tid; c < HT_ROWS * (HT_K / 8); c += 128) {              // 16-byte pieces; K and N are multiples of 8
+            const int r = c / (HT_K / 8), cc = (c % (HT_K / 8)) * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (t0 + r < n_tokens && k0 + cc < K) v = *reinterpret_cast<const uint4*>(a_base + (size_t)(t0 + r) * ld_in + k0 + cc);
+            *reinterpret_cast<uint4*>(&sA[r][cc]) = v;
+        }
+        for (int c = tid; c < HT_K * (HT_COLS / 8); c += 128) {
+            const int r = c / (HT_COLS / 8), cc = (c % (HT_COLS / 8)) * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (k0 + r < K && n0 + cc < N) v = *reinterpret_cast<const uint4*>(w_base + (size_t)(k0 + r) * N + n0 + cc);
+            *reinterpret_cast<uint4*>(&sW[r][cc]) = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HT_K; kk += 16) {
+            uint32_t a[4];
+            ldsm_x4(a, &sA[warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][kk + 8 * (lane >> 4)]);
+#pragma unroll
+            for (int j = 0; j < HT_COLS / 8; j += 2) {
+                uint32_t bb[4];
+                ldsm_x4_trans(bb, &sW[kk + (lane & 7) + 8 * ((lane >> 3) & 1)][(j + (lane >> 4)) * 8]);
+                mma_bf16(acc[j], a, bb[0], bb[1]);
+                mma_bf16(acc[j + 1], a, bb[2], bb[3]);
+            }
+        }
+    }
+    const int r0 = t0 + warp * 16 + (lane >> 2);
+#pragma unroll
+    for (int j = 0; j < HT_COLS / 8; j++) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int t = r0 + 8 * (e >> 1), n = n0 + j * 8 + 2 * (lane & 3) + (e & 1);
+            if (t < n_tokens && n < N) {
+                float v = acc[j][e];
+                if (gate != nullptr) v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * ld_gate + gate_off + (size_t)h * N + n])));
+                out[(size_t)t * ld_out + out_off + (size_t)h * out_stride + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------- a product with a weight per head -----
 // out[t, h, n] = sum_k in[t, h, k] * W_h[k, n]  (W stored [H][K][N]), optionally times sigmoid(gate[t, h * N + n]).
 // A block takes HL_TT tokens of one head and 128 output columns; its inputs sit in shared memory as 32-bit numbers.
@@ -173,6 +257,14 @@ GFB_API int gfb_headwise_linear(const void* in, int dt, int ld_in, int in_off, i
     if (n_tokens <= 0 || H <= 0 || N <= 0) return 0;
     if (K <= 0) return gfb_fail("gfb_headwise_linear: K = %d", K);
     if (H > 65535 || (N + HL_COLS - 1) / HL_COLS > 65535) return gfb_fail("gfb_headwise_linear: %d heads of %d columns exceed the grid limit", H, N);
+    if (dt == GFB_BF16 && K % 16 == 0 && N % 8 == 0 && ld_in % 8 == 0 && in_off % 8 == 0 && in_stride % 8 == 0 &&
+        (((uintptr_t)in | (uintptr_t)w) & 15) == 0) {
+        dim3 grid((n_tokens + HT_ROWS - 1) / HT_ROWS, H, (N + HT_COLS - 1) / HT_COLS);
+        cudaError_t e = gfb_launch(headwise_linear_tc_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)in, ld_in, in_off, in_stride,
+                                   (const __nv_bfloat16*)w, (__nv_bfloat16*)out, ld_out, out_off, out_stride, (const __nv_bfloat16*)gate,
+                                   ld_gate, gate_off, n_tokens, K, N);
+        return gfb_check(e, "gfb_headwise_linear (tensor cores)");
+    }
     const size_t smem = ((size_t)HL_TT * K + (size_t)HL_KS * HL_TT * HL_COLS) * sizeof(float);
     if (smem > 160 * 1024) return gfb_fail("gfb_headwise_linear: K = %d does not fit shared memory", K);
     dim3 grid((n_tokens + HL_TT - 1) / HL_TT, H, (N + HL_COLS - 1) / HL_COLS);
@@ -207,32 +299,11 @@ constexpr int LA_KEYS = 32;           // cached rows per tile
 constexpr int LA_THREADS = 256;
 constexpr int LA_PAD = 8;             // bfloat16 numbers of padding per shared-memory row: ldmatrix rows fall into distinct banks
 
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
-    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
-}
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
-    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
 // NT: value n-tiles (of 8 columns) a warp may hold: rank / 2 <= 8 * NT
 template <int NT>
 __global__ void __launch_bounds__(LA_THREADS, 1)
 latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, GfbPagedKV kv, GfbBatch b,
-                        int H, int Dk, int R, float scale_log2, int* status) {
+                        int H, int Dk, int R, float scale_log2, int n_splits, float* __restrict__ partial, int* status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int DkP = Dk + LA_PAD;
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [LA_ROWS][DkP]
@@ -246,7 +317,10 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
     const int slot = b.slots[s], start = b.lengths[slot];
     const int rows_here = min(LA_ROWS, n_rows - m0);
     const int last_pos = start + (m0 + rows_here - 1) / H;                      // the latest position any row of the block sees
-    const int n_tiles = last_pos / LA_KEYS + 1;
+    const int all_tiles = last_pos / LA_KEYS + 1;
+    // with n_splits > 1 (a decode step) the block takes one slice of the cached rows and leaves its unnormalised sums
+    const int per_split = (all_tiles + n_splits - 1) / n_splits;
+    const int tile_lo = blockIdx.z * per_split, n_tiles = min(all_tiles, tile_lo + per_split);
     const int* pt = kv.page_table + (size_t)slot * kv.max_pages;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int chunks = Dk / 8;                                                  // 16-byte pieces of a row
@@ -268,7 +342,7 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    load_keys(0, 0);
+    if (tile_lo < n_tiles) load_keys(tile_lo & 1, tile_lo);
     // the block's query rows (rows beyond the sequence's are zero)
     const __nv_bfloat16* qsrc = q + ((size_t)t0 * H + m0) * Dk;
     for (int c = tid; c < LA_ROWS * chunks; c += LA_THREADS) {
@@ -288,7 +362,8 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
     for (int j = 0; j < NT; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float mx0 = -INFINITY, mx1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    for (int tile = 0; tile < n_tiles; tile++) {
+    if (tile_lo >= n_tiles) __syncthreads();            // (an empty slice still leaves its neutral sums below)
+    for (int tile = tile_lo; tile < n_tiles; tile++) {
         const int stage = tile & 1;
         if (tile + 1 < n_tiles) {
             load_keys(stage ^ 1, tile + 1);
@@ -373,6 +448,24 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
         }
         __syncthreads();                               // the stage is free for the tile after next
     }
+    if (n_splits > 1) {
+        // [row][split][R values, maximum (base-2 exponent), sum]
+        float* base = partial + (((size_t)t0 * H + m0) * n_splits + blockIdx.z) * (R + 2);
+        const size_t row_stride = (size_t)n_splits * (R + 2);
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+            if (j < nt_n) {
+                const int col = (nt_lo + j) * 8 + 2 * (lane & 3);
+                if (r0 < rows_here) *reinterpret_cast<float2*>(base + (size_t)r0 * row_stride + col) = make_float2(o[j][0], o[j][1]);
+                if (r0 + 8 < rows_here) *reinterpret_cast<float2*>(base + (size_t)(r0 + 8) * row_stride + col) = make_float2(o[j][2], o[j][3]);
+            }
+        }
+        if (half == 0 && (lane & 3) == 0) {
+            if (r0 < rows_here) { base[(size_t)r0 * row_stride + R] = mx0; base[(size_t)r0 * row_stride + R + 1] = l0; }
+            if (r0 + 8 < rows_here) { base[(size_t)(r0 + 8) * row_stride + R] = mx1; base[(size_t)(r0 + 8) * row_stride + R + 1] = l1; }
+        }
+        return;
+    }
     const float i0 = l0 > 0.f ? 1.0f / l0 : 0.f, i1 = l1 > 0.f ? 1.0f / l1 : 0.f;
     __nv_bfloat16* orow = out + ((size_t)t0 * H + m0) * R;
 #pragma unroll
@@ -385,12 +478,38 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
     }
 }
 
+// The slices of a row: out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M the largest m_s, slices in ascending order.
+__global__ void latent_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int n_splits, int R) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const size_t row = blockIdx.x;
+    const float* base = partial + row * n_splits * (R + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; s++) M = fmaxf(M, base[(size_t)s * (R + 2) + R]);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+        const float m = base[(size_t)s * (R + 2) + R];
+        if (m != -INFINITY) l += base[(size_t)s * (R + 2) + R + 1] * exp2f(m - M);
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < n_splits; s++) {
+            const float m = base[(size_t)s * (R + 2) + R];
+            if (m != -INFINITY) v += base[(size_t)s * (R + 2) + c] * exp2f(m - M);
+        }
+        out[row * R + c] = __float2bfloat16_rn(v * inv);
+    }
+}
+
 // q bfloat16 [T, H, Dk] (Dk = rank + rot), out bfloat16 [T, H * rank]; the cache entry holds one row of Dk numbers per
-// token in pages of a multiple of 32 tokens.  Needs Dk % 16 == 0, rank % 16 == 0, rank <= 512, rank < Dk.
+// token in pages of a multiple of 32 tokens.  Needs Dk % 16 == 0, rank % 16 == 0, rank <= 512, rank < Dk.  n_splits > 1:
+// every sequence's cached rows are cut into that many slices with a block each, whose sums go through `partial`
+// (float32 [T * H, n_splits, rank + 2]) and a second kernel.
 GFB_API int gfb_latent_attention(const void* q, void* out, void* k_pool, const int* page_table, int max_pages, int page_size,
                                  int n_pages, const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths,
-                                 int n_seqs, int n_tokens, int max_q_len, int H, int Dk, int R, float scale, int* status,
-                                 cudaStream_t stream) {
+                                 int n_seqs, int n_tokens, int max_q_len, int H, int Dk, int R, float scale, int n_splits,
+                                 float* partial, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (Dk % 16 || R % 16 || R > 512 || R >= Dk || page_size % LA_KEYS)
         return gfb_fail("gfb_latent_attention: rows of %d with %d value columns in pages of %d do not fit the kernel", Dk, R, page_size);
@@ -401,7 +520,9 @@ GFB_API int gfb_latent_attention(const void* q, void* out, void* k_pool, const i
     if (smem > 220 * 1024) return gfb_fail("gfb_latent_attention: rows of %d numbers do not fit shared memory", Dk);
     const long tiles = ((long)max_q_len * H + LA_ROWS - 1) / LA_ROWS;
     if (tiles > 65535) return gfb_fail("gfb_latent_attention: %ld row tiles exceed the grid limit", tiles);
-    dim3 grid(n_seqs, (unsigned)tiles);
+    if (n_splits < 1) n_splits = 1;
+    if (n_splits > 1 && partial == nullptr) return gfb_fail("gfb_latent_attention: slices need room for their sums");
+    dim3 grid(n_seqs, (unsigned)tiles, n_splits);
     const float scale_log2 = scale * 1.4426950408889634f;
     const int nt = (R / 8 + 1) / 2;
     cudaError_t e;
@@ -410,11 +531,15 @@ GFB_API int gfb_latent_attention(const void* q, void* out, void* k_pool, const i
         e = cudaFuncSetAttribute(latent_attention_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
         if (e != cudaSuccess) return gfb_fail("gfb_latent_attention: %s", cudaGetErrorString(e));                           \
         e = gfb_launch(latent_attention_kernel<NT>, grid, dim3(LA_THREADS), smem, stream, (const __nv_bfloat16*)q,          \
-                       (__nv_bfloat16*)out, kv, b, H, Dk, R, scale_log2, status);                                           \
+                       (__nv_bfloat16*)out, kv, b, H, Dk, R, scale_log2, n_splits, partial, status);                        \
     } while (0)
     if (nt <= 8) GO(8);
     else if (nt <= 16) GO(16);
     else GO(32);
 #undef GO
-    return gfb_check(e, "gfb_latent_attention");
+    if (gfb_check(e, "gfb_latent_attention")) return 1;
+    if (n_splits == 1) return 0;
+    e = gfb_launch(latent_combine_kernel, dim3((unsigned)n_tokens * H), dim3(128), 0, stream, (const float*)partial, (__nv_bfloat16*)out,
+                   n_splits, R);
+    return gfb_check(e, "gfb_latent_attention (combine)");
 }

@@ -114,7 +114,8 @@ GFB_API int gfb_short_conv(const void* src, int dt, int ld, int col_off, int C, 
 // the sequence's tokens of this step.  The rows are dealt in groups of RPT to RG lanes of a warp (RG a power of two),
 // a warp holds 32 / RG columns, a block four warps.  A sum over the rows is RPT terms per lane in ascending order and
 // then a butterfly over the RG lanes: no barrier per token.  The inputs of TB tokens are staged in shared memory at a
-// time (row vectors padded by one number per group so that the RG lanes read distinct banks).
+// time (row vectors padded by one number per group so that the RG lanes read distinct banks), in two stages: the next
+// tile's copies (cp.async) run under the current tile's steps.
 constexpr int TB = 16;
 constexpr int SCAN_WARPS = 4;
 
@@ -123,6 +124,14 @@ __device__ __forceinline__ float group_sum(float v, int RG) {
     return v;
 }
 __device__ __forceinline__ int padded(int c, int RPT) { return c + c / RPT; }      // index of row c in a padded row vector
+// One 32-bit number from global to shared memory without passing a register: a tile's copies are all in flight at once
+// and the next tile's run under the current tile's steps.
+__device__ __forceinline__ void copy_async4(float* smem, const float* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(gmem));
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // x [T, ldx] float32: head h's P inputs at column h * P, group g's N numbers of B at b_off + g * N, of C at
 // c_off + g * N.  dt_raw: [T, ld_dt] of type TD, head h at column dt_off + h.
@@ -137,12 +146,8 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
     gfb_pdl_wait();
     const int s = blockIdx.x, h = blockIdx.y, g = h / (H / G);
     const int CW = 32 / RG, CB = SCAN_WARPS * CW, NP = RG * (RPT + 1);
-    float* sB = sm;                       // [TB][NP]
-    float* sC = sB + TB * NP;             // [TB][NP]
-    float* sX = sC + TB * NP;             // [TB][CB]
-    float* sO = sX + TB * CB;             // [TB][CB]
-    float* sDt = sO + TB * CB;            // [TB]
-    float* sA = sDt + TB;                 // [TB]
+    const int STAGE = TB * (2 * NP + CB + 2);
+    float* sO = sm + 2 * STAGE;           // [TB][CB]; ahead of it two stages of: B [TB][NP], C [TB][NP], x [TB][CB], dt [TB], decay [TB]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int rgi = lane % RG, cl = warp * CW + lane / RG;           // row group, column within the block
     const int p0 = blockIdx.z * CB, p = p0 + cl;
@@ -156,25 +161,52 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
         st[r] = (active && n < N) ? S[(size_t)n * P + p] : 0.f;
     }
     const float bias = ldw(dt_bias, w_dt, h), rate = expf(ldw(a_log, w_dt, h)), dskip = skip != nullptr ? ldw(skip, w_dt, h) : 0.f;
-    for (int tile = t0; tile < t1; tile += TB) {
+    // rows and columns beyond the state's stay zero: clear the token rows this step will use, in the stages it will use
+    {
+        const int used = min(TB, t1 - t0), stages = t1 - t0 > TB ? 2 : 1;
+        for (int st_ = 0; st_ < stages; st_++) {
+            float* base = sm + st_ * STAGE;
+            for (int i = tid; i < used * NP; i += blockDim.x) { base[i] = 0.f; base[TB * NP + i] = 0.f; }
+            for (int i = tid; i < used * CB; i += blockDim.x) base[2 * TB * NP + i] = 0.f;
+        }
+    }
+    __syncthreads();
+    float dt_next = 0.f;
+    auto fetch = [&](int stage, int tile) {
+        float* base = sm + stage * STAGE;
         const int nt = min(TB, t1 - tile);
-        __syncthreads();                                       // the previous tile's outputs are written
-        for (int i = tid; i < nt * RG * RPT; i += blockDim.x) {
-            const int tt = i / (RG * RPT), n = i - tt * RG * RPT;
+        for (int tt = warp; tt < nt; tt += SCAN_WARPS) {
             const float* row = x + (size_t)(tile + tt) * ldx;
-            sB[tt * NP + padded(n, RPT)] = n < N ? row[b_off + g * N + n] : 0.f;
-            sC[tt * NP + padded(n, RPT)] = n < N ? row[c_off + g * N + n] : 0.f;
+            for (int n = lane; n < N; n += 32) {
+                copy_async4(base + tt * NP + padded(n, RPT), row + b_off + g * N + n);
+                copy_async4(base + TB * NP + tt * NP + padded(n, RPT), row + c_off + g * N + n);
+            }
+            for (int q = lane; q < CB && p0 + q < P; q += 32) copy_async4(base + 2 * TB * NP + tt * CB + q, row + (size_t)h * P + p0 + q);
         }
-        for (int i = tid; i < nt * CB; i += blockDim.x) {
-            const int tt = i / CB, q = i - tt * CB;
-            sX[tt * CB + q] = p0 + q < P ? x[(size_t)(tile + tt) * ldx + (size_t)h * P + p0 + q] : 0.f;
-        }
+        copy_commit();
+        if (tid < nt) dt_next = gfb_to_f32(dt_raw[(size_t)(tile + tid) * ld_dt + dt_off + h]);
+    };
+    if (t0 < t1) fetch(0, t0);
+    int stage = 0;
+    for (int tile = t0; tile < t1; tile += TB, stage ^= 1) {
+        const int nt = min(TB, t1 - tile);
+        float* sB = sm + stage * STAGE;
+        float* sC = sB + TB * NP;
+        float* sX = sC + TB * NP;
+        float* sDt = sX + TB * CB;
+        float* sA = sDt + TB;
         if (tid < nt) {
-            const float d = softplus_f(gfb_to_f32(dt_raw[(size_t)(tile + tid) * ld_dt + dt_off + h]) + bias);
+            const float d = softplus_f(dt_next + bias);
             sDt[tid] = d;
             sA[tid] = expf(-rate * d);
         }
-        __syncthreads();
+        if (tile + TB < t1) {
+            fetch(stage ^ 1, tile + TB);                       // runs under this tile's steps
+            copy_wait<1>();
+        } else {
+            copy_wait<0>();
+        }
+        __syncthreads();                                       // this tile's inputs have landed; the previous outputs are written
         for (int tt = 0; tt < nt; tt++) {
             const float a = sA[tt], dx = sDt[tt], xp = sX[tt * CB + cl];
             const float* bb = sB + tt * NP + rgi * (RPT + 1);
@@ -189,10 +221,10 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
             if (rgi == 0) sO[tt * CB + cl] = acc + dskip * xp;
         }
         __syncthreads();
-        for (int i = tid; i < nt * CB; i += blockDim.x) {
-            const int tt = i / CB, q = i - tt * CB;
-            if (p0 + q < P) out[(size_t)(tile + tt) * H * P + (size_t)h * P + p0 + q] = sO[tt * CB + q];
-        }
+        for (int tt = warp; tt < nt; tt += SCAN_WARPS)
+            for (int q = lane; q < CB; q += 32)
+                if (p0 + q < P) out[(size_t)(tile + tt) * H * P + (size_t)h * P + p0 + q] = sO[tt * CB + q];
+        // the next pass's barrier comes before any lane writes sO or this stage again
     }
     if (active) {
 #pragma unroll
@@ -203,26 +235,45 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
     }
 }
 
-// qkv [T, ldq] float32 (convolved, activated): query head j at q_off + j * d, key head j at k_off + j * d, value head
-// h at v_off + h * dv.  beta_raw [T, ld_b] of type TD, head h at column beta_off + h.  a_raw [T, ld_a] float32, head
-// h's d channels at a_off + h * d; dt_bias [H * d].
+// What does not depend on the state is done for all tokens at once, in place: q and k become unit vectors per head
+// (q also times q_scale), the decay inputs become the decays g = exp(-exp(A_log_h) softplus(a + dt_bias)).
+__global__ void delta_prepare_kernel(float* __restrict__ qkv, int ldq, int q_off, int k_off, float* __restrict__ a_raw, int ld_a,
+                                     int a_off, const void* __restrict__ dt_bias, const void* __restrict__ a_log, int w_dt, int H,
+                                     int KH, int d, float q_scale, float unit_eps) {
+    gfb_pdl_launch();
+    gfb_pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int item = warp; item < 2 * KH; item += nwarp) {
+        float* vec = qkv + (size_t)t * ldq + (item & 1 ? k_off : q_off) + (size_t)(item >> 1) * d;
+        float ss = 0.f;
+        for (int c = lane; c < d; c += 32) ss = fmaf(vec[c], vec[c], ss);
+        ss = gfb_warp_sum(ss);
+        const float f = (1.0f / sqrtf(ss + unit_eps)) * (item & 1 ? 1.0f : q_scale);
+        for (int c = lane; c < d; c += 32) vec[c] *= f;
+    }
+    float* ar = a_raw + (size_t)t * ld_a + a_off;
+    for (int h = 0; h < H; h++) {
+        const float rate = expf(ldw(a_log, w_dt, h));
+        for (int c = threadIdx.x; c < d; c += blockDim.x)
+            ar[(size_t)h * d + c] = expf(-rate * softplus_f(ar[(size_t)h * d + c] + ldw(dt_bias, w_dt, (size_t)h * d + c)));
+    }
+}
+
+// qkv [T, ldq] float32 (convolved, activated, q and k unit vectors): query head j at q_off + j * d, key head j at
+// k_off + j * d, value head h at v_off + h * dv.  beta_raw [T, ld_b] of type TD, head h at column beta_off + h.
+// decay [T, ld_a] float32, head h's d channels at a_off + h * d.
 template <typename TD, int RPT>
 __global__ void __launch_bounds__(32 * SCAN_WARPS)
 delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, int v_off, const TD* __restrict__ beta_raw, int ld_b,
-                  int beta_off, const float* __restrict__ a_raw, int ld_a, int a_off, const void* __restrict__ dt_bias,
-                  const void* __restrict__ a_log, int w_dt, float* __restrict__ state, size_t state_ld, float* __restrict__ out,
-                  GfbBatch b, int H, int KH, int d, int dv, float q_scale, float unit_eps, int RG) {
+                  int beta_off, const float* __restrict__ decay, int ld_a, int a_off, float* __restrict__ state, size_t state_ld,
+                  float* __restrict__ out, GfbBatch b, int H, int KH, int d, int dv, int RG) {
     extern __shared__ float sm[];
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int s = blockIdx.x, h = blockIdx.y, kh = h / (H / KH);
     const int CW = 32 / RG, CB = SCAN_WARPS * CW, NP = RG * (RPT + 1);
-    float* sQ = sm;                       // [TB][NP]
-    float* sK = sQ + TB * NP;             // [TB][NP]
-    float* sG = sK + TB * NP;             // [TB][NP]
-    float* sV = sG + TB * NP;             // [TB][CB]
-    float* sO = sV + TB * CB;             // [TB][CB]
-    float* sBeta = sO + TB * CB;          // [TB]
+    const int STAGE = TB * (3 * NP + CB + 1);
+    float* sO = sm + 2 * STAGE;           // [TB][CB]; ahead of it two stages of: q, k, decay [TB][NP] each, v [TB][CB], beta [TB]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int rgi = lane % RG, cl = warp * CW + lane / RG;
     const int p0 = blockIdx.z * CB, p = p0 + cl;
@@ -235,39 +286,51 @@ delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, 
         const int i = rgi * RPT + r;
         st[r] = (active && i < d) ? S[(size_t)i * dv + p] : 0.f;
     }
-    const float rate = expf(ldw(a_log, w_dt, h));
-    for (int tile = t0; tile < t1; tile += TB) {
+    // rows and columns beyond the state's stay zero: clear the token rows this step will use, in the stages it will use
+    {
+        const int used = min(TB, t1 - t0), stages = t1 - t0 > TB ? 2 : 1;
+        for (int st_ = 0; st_ < stages; st_++) {
+            float* base = sm + st_ * STAGE;
+            for (int i = tid; i < used * NP; i += blockDim.x) { base[i] = 0.f; base[TB * NP + i] = 0.f; base[2 * TB * NP + i] = 0.f; }
+            for (int i = tid; i < used * CB; i += blockDim.x) base[3 * TB * NP + i] = 0.f;
+        }
+    }
+    __syncthreads();
+    float beta_next = 0.f;
+    auto fetch = [&](int stage, int tile) {
+        float* base = sm + stage * STAGE;
         const int nt = min(TB, t1 - tile);
-        __syncthreads();
-        for (int i = tid; i < nt * RG * RPT; i += blockDim.x) {
-            const int tt = i / (RG * RPT), c = i - tt * RG * RPT;
-            const int at = tt * NP + padded(c, RPT);
-            if (c < d) {
-                const float* row = qkv + (size_t)(tile + tt) * ldq;
-                sQ[at] = row[q_off + kh * d + c];
-                sK[at] = row[k_off + kh * d + c];
-                const float a = a_raw[(size_t)(tile + tt) * ld_a + a_off + (size_t)h * d + c] + ldw(dt_bias, w_dt, (size_t)h * d + c);
-                sG[at] = expf(-rate * softplus_f(a));
-            } else {
-                sQ[at] = 0.f; sK[at] = 0.f; sG[at] = 1.f;
+        for (int tt = warp; tt < nt; tt += SCAN_WARPS) {
+            const float* row = qkv + (size_t)(tile + tt) * ldq;
+            const float* grow = decay + (size_t)(tile + tt) * ld_a + a_off + (size_t)h * d;
+            for (int c = lane; c < d; c += 32) {
+                const int at = tt * NP + padded(c, RPT);
+                copy_async4(base + at, row + q_off + kh * d + c);
+                copy_async4(base + TB * NP + at, row + k_off + kh * d + c);
+                copy_async4(base + 2 * TB * NP + at, grow + c);
             }
+            for (int c = lane; c < CB && p0 + c < dv; c += 32) copy_async4(base + 3 * TB * NP + tt * CB + c, row + v_off + (size_t)h * dv + p0 + c);
         }
-        for (int i = tid; i < nt * CB; i += blockDim.x) {
-            const int tt = i / CB, c = i - tt * CB;
-            sV[tt * CB + c] = p0 + c < dv ? qkv[(size_t)(tile + tt) * ldq + v_off + (size_t)h * dv + p0 + c] : 0.f;
+        copy_commit();
+        if (tid < nt) beta_next = gfb_to_f32(beta_raw[(size_t)(tile + tid) * ld_b + beta_off + h]);
+    };
+    if (t0 < t1) fetch(0, t0);
+    int stage = 0;
+    for (int tile = t0; tile < t1; tile += TB, stage ^= 1) {
+        const int nt = min(TB, t1 - tile);
+        float* sQ = sm + stage * STAGE;
+        float* sK = sQ + TB * NP;
+        float* sG = sK + TB * NP;
+        float* sV = sG + TB * NP;
+        float* sBeta = sV + TB * CB;
+        if (tid < nt) sBeta[tid] = sigmoid_f(beta_next);
+        if (tile + TB < t1) {
+            fetch(stage ^ 1, tile + TB);                       // runs under this tile's steps
+            copy_wait<1>();
+        } else {
+            copy_wait<0>();
         }
-        if (tid < nt) sBeta[tid] = sigmoid_f(gfb_to_f32(beta_raw[(size_t)(tile + tid) * ld_b + beta_off + h]));
-        __syncthreads();
-        // unit vectors: a warp per (token, q or k); lanes add strided squares, a fixed tree adds the lanes
-        for (int item = warp; item < 2 * nt; item += SCAN_WARPS) {
-            float* vec = (item & 1 ? sK : sQ) + (item >> 1) * NP;
-            float ss = 0.f;
-            for (int c = lane; c < d; c += 32) { const float v = vec[padded(c, RPT)]; ss = fmaf(v, v, ss); }
-            ss = gfb_warp_sum(ss);
-            const float f = (1.0f / sqrtf(ss + unit_eps)) * (item & 1 ? 1.0f : q_scale);
-            for (int c = lane; c < d; c += 32) vec[padded(c, RPT)] *= f;
-        }
-        __syncthreads();
+        __syncthreads();                                       // this tile's inputs have landed; the previous outputs are written
         for (int tt = 0; tt < nt; tt++) {
             const float* gg = sG + tt * NP + rgi * (RPT + 1);
             const float* kk = sK + tt * NP + rgi * (RPT + 1);
@@ -292,10 +355,9 @@ delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, 
             if (rgi == 0) sO[tt * CB + cl] = o;
         }
         __syncthreads();
-        for (int i = tid; i < nt * CB; i += blockDim.x) {
-            const int tt = i / CB, c = i - tt * CB;
-            if (p0 + c < dv) out[(size_t)(tile + tt) * H * dv + (size_t)h * dv + p0 + c] = sO[tt * CB + c];
-        }
+        for (int tt = warp; tt < nt; tt += SCAN_WARPS)
+            for (int c = lane; c < CB; c += 32)
+                if (p0 + c < dv) out[(size_t)(tile + tt) * H * dv + (size_t)h * dv + p0 + c] = sO[tt * CB + c];
     }
     if (active) {
 #pragma unroll
@@ -306,11 +368,13 @@ delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, 
     }
 }
 
-// rows per lane and lanes per column for a state of `rows` rows: the fewest rows per lane that need at most 32 lanes;
-// 0 if none does
-static int pick_rpt(int rows, int* rg) {
-    const int rpt[3] = {16, 32, 64};
-    for (int i = 0; i < 3; i++) {
+// rows per lane and lanes per column for a state of `rows` rows: the fewest rows per lane that need at most 32 lanes
+// (a token's step is a chain of dependent instructions, so few rows per lane and many lanes per column make it short;
+// 128 rows: 8 rows on each of 16 lanes took 0.27 us per token where 16 rows on 8 lanes took 1.0); 0 if none does
+static int pick_rpt(int rows, int* rg, bool many_blocks) {
+    // with hundreds of (sequence, head) pairs the SMs are busy anyway: 16 rows per lane then halve the number of blocks
+    const int rpt[4] = {8, 16, 32, 64};
+    for (int i = many_blocks ? 1 : 0; i < 4; i++) {
         const int need = (rows + rpt[i] - 1) / rpt[i];
         if (need <= 32) {
             int g = 1;
@@ -341,12 +405,12 @@ GFB_API int gfb_ssd_scan(const float* x, int ldx, int b_off, int c_off, const vo
     if (n_tokens <= 0) return 0;
     if (G <= 0 || H % G) return gfb_fail("gfb_ssd_scan: %d heads do not divide into %d groups", H, G);
     int RG = 0;
-    const int rpt = pick_rpt(N, &RG);
+    const int rpt = pick_rpt(N, &RG, (long)n_seqs * H >= 512);
     if (!rpt) return gfb_fail("gfb_ssd_scan: a state of %d rows per head does not fit a warp", N);
     const int CB = SCAN_WARPS * (32 / RG);
     const unsigned slices = (unsigned)((P + CB - 1) / CB);
     if (H > 65535 || slices > 65535) return gfb_fail("gfb_ssd_scan: %d heads of %d columns exceed the grid limit", H, P);
-    const size_t smem = ((size_t)TB * (2 * RG * (rpt + 1) + 2 * CB + 2)) * sizeof(float);
+    const size_t smem = ((size_t)2 * TB * (2 * RG * (rpt + 1) + CB + 2) + (size_t)TB * CB) * sizeof(float);
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     cudaError_t e = cudaSuccess;
 #define GO(TD, R)                                                                                                          \
@@ -355,7 +419,7 @@ GFB_API int gfb_ssd_scan(const float* x, int ldx, int b_off, int c_off, const vo
         e = gfb_launch(ssd_scan_kernel<TD, R>, dim3(n_seqs, H, slices), dim3(32 * SCAN_WARPS), smem, stream, x, ldx, b_off, c_off, \
                        (const TD*)dt_raw, ld_dt, dt_off, dt_bias, a_log, skip, w_dt, state, (size_t)state_ld, out, b, H, P, N, G, RG); \
     } while (0)
-#define PICK(TD) do { if (rpt == 16) GO(TD, 16); else if (rpt == 32) GO(TD, 32); else GO(TD, 64); } while (0)
+#define PICK(TD) do { if (rpt == 8) GO(TD, 8); else if (rpt == 16) GO(TD, 16); else if (rpt == 32) GO(TD, 32); else GO(TD, 64); } while (0)
     if (dt_dt == GFB_BF16) PICK(__nv_bfloat16);
     else if (dt_dt == GFB_F32) PICK(float);
     else return gfb_fail("gfb_ssd_scan: unknown type %d", dt_dt);
@@ -365,30 +429,33 @@ GFB_API int gfb_ssd_scan(const float* x, int ldx, int b_off, int c_off, const vo
 }
 
 // state float32: slot stride state_ld, per slot [H][d][dv]; out float32 [T, H, dv]; dt_bias [H * d], a_log [H] of w_dt.
-GFB_API int gfb_delta_rule(const float* qkv, int ldq, int q_off, int k_off, int v_off, const void* beta_raw, int b_dt, int ld_b,
-                           int beta_off, const float* a_raw, int ld_a, int a_off, const void* dt_bias, const void* a_log, int w_dt,
+// qkv and a_raw are scratch of the caller: q and k are overwritten by their unit vectors, the decay inputs by the decays.
+GFB_API int gfb_delta_rule(float* qkv, int ldq, int q_off, int k_off, int v_off, const void* beta_raw, int b_dt, int ld_b,
+                           int beta_off, float* a_raw, int ld_a, int a_off, const void* dt_bias, const void* a_log, int w_dt,
                            float* state, long state_ld, float* out, const int* cu_seqlens, const int* tok_seq, const int* slots,
                            const int* lengths, int n_seqs, int n_tokens, int H, int KH, int d, int dv, float q_scale,
                            float unit_eps, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (KH <= 0 || H % KH) return gfb_fail("gfb_delta_rule: %d heads do not divide into %d query/key heads", H, KH);
     int RG = 0;
-    const int rpt = pick_rpt(d, &RG);
+    const int rpt = pick_rpt(d, &RG, (long)n_seqs * H >= 512);
     if (!rpt) return gfb_fail("gfb_delta_rule: a state of %d rows per head does not fit a warp", d);
     const int CB = SCAN_WARPS * (32 / RG);
     const unsigned slices = (unsigned)((dv + CB - 1) / CB);
     if (H > 65535 || slices > 65535) return gfb_fail("gfb_delta_rule: %d heads of %d columns exceed the grid limit", H, dv);
-    const size_t smem = ((size_t)TB * (3 * RG * (rpt + 1) + 2 * CB + 1)) * sizeof(float);
+    const size_t smem = ((size_t)2 * TB * (3 * RG * (rpt + 1) + CB + 1) + (size_t)TB * CB) * sizeof(float);
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
-    cudaError_t e = cudaSuccess;
+    cudaError_t e = gfb_launch(delta_prepare_kernel, dim3(n_tokens), dim3(128), 0, stream, qkv, ldq, q_off, k_off, a_raw, ld_a, a_off,
+                               dt_bias, a_log, w_dt, H, KH, d, q_scale, unit_eps);
+    if (gfb_check(e, "gfb_delta_rule (prepare)")) return 1;
 #define GO(TD, R)                                                                                                          \
     do {                                                                                                                   \
         if (allow_smem(delta_rule_kernel<TD, R>, smem, "gfb_delta_rule")) return 1;                                        \
-        e = gfb_launch(delta_rule_kernel<TD, R>, dim3(n_seqs, H, slices), dim3(32 * SCAN_WARPS), smem, stream, qkv, ldq, q_off, k_off, \
-                       v_off, (const TD*)beta_raw, ld_b, beta_off, a_raw, ld_a, a_off, dt_bias, a_log, w_dt, state,        \
-                       (size_t)state_ld, out, b, H, KH, d, dv, q_scale, unit_eps, RG);                                     \
+        e = gfb_launch(delta_rule_kernel<TD, R>, dim3(n_seqs, H, slices), dim3(32 * SCAN_WARPS), smem, stream, (const float*)qkv, ldq, \
+                       q_off, k_off, v_off, (const TD*)beta_raw, ld_b, beta_off, (const float*)a_raw, ld_a, a_off, state,  \
+                       (size_t)state_ld, out, b, H, KH, d, dv, RG);                                                        \
     } while (0)
-#define PICK(TD) do { if (rpt == 16) GO(TD, 16); else if (rpt == 32) GO(TD, 32); else GO(TD, 64); } while (0)
+#define PICK(TD) do { if (rpt == 8) GO(TD, 8); else if (rpt == 16) GO(TD, 16); else if (rpt == 32) GO(TD, 32); else GO(TD, 64); } while (0)
     if (b_dt == GFB_BF16) PICK(__nv_bfloat16);
     else if (b_dt == GFB_F32) PICK(float);
     else return gfb_fail("gfb_delta_rule: unknown type %d", b_dt);

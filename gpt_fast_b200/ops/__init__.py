@@ -178,7 +178,9 @@ def delta_rule(qkv, offsets, beta_src, beta_off: int, a_src, a_off: int, dt_bias
     g = exp(-exp(a_log[h]) softplus(a_src[:, a_off + h * head_dim + i] + dt_bias[h * head_dim + i])):
     S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
     qkv float32 [T, W] with q, k, v at the column offsets `offsets`; a_src float32; state float32 [n_slots, S] holds
-    [n_head, head_dim, v_head_dim] per sequence from column state_off; out float32 [T, n_head, v_head_dim]."""
+    [n_head, head_dim, v_head_dim] per sequence from column state_off; out float32 [T, n_head, v_head_dim].
+    qkv and a_src are the caller's scratch: the kernels overwrite q and k by their unit vectors and the decay inputs by the
+    decays."""
     return kernels().delta_rule(qkv, offsets, beta_src, beta_off, a_src, a_off, dt_bias, a_log, state, state_off, out, batch,
                                 n_head, n_qk, head_dim, v_head_dim, q_scale, unit_eps)
 

@@ -580,10 +580,18 @@ class CudaKernels:
                 and (64 + 2 * 32) * (head_dim + 8) * 2 <= 220 * 1024):
             # a latent that all heads share: the tensor-core kernel that fetches every cached row once per 64 (token, head)
             # pairs of a sequence (a decode step's heads are the rows of one MMA)
+            splits, scratch = 1, None
+            if batch.max_q_len == 1:
+                # a decode step: slices of at least 128 cached rows, as many as keep about four blocks per SM busy
+                splits = max(1, min(16, -(-int(batch.max_kv_len) // 32) // 4))
+                while splits > 1 and batch.n_seqs * -(-n_head // 64) * splits > 4 * self.sm_count:
+                    splits //= 2
+                if splits > 1:
+                    scratch = torch.empty(T * n_head * splits * (dv + 2), dtype=torch.float32, device=q.device)
             return self._call("latent", "gfb_latent_attention", _ptr(q), _ptr(out), _ptr(kv.k_pool), _ptr(kv.page_table),
                               c_int(kv.page_table.shape[1]), c_int(kv.page_size), c_int(kv.k_pool.shape[0]), *self._batch_args(batch),
-                              c_int(int(batch.max_q_len)), c_int(n_head), c_int(head_dim), c_int(dv), c_float(scale), _ptr(batch.status),
-                              _stream())
+                              c_int(int(batch.max_q_len)), c_int(n_head), c_int(head_dim), c_int(dv), c_float(scale), c_int(splits),
+                              _ptr(scratch), _ptr(batch.status), _stream())
         if (not values_in_keys and dv == head_dim and q.dtype == torch.bfloat16 and kv.page_size == 64 and n_head // n_kv <= 8
                 and (head_dim in (64, 128) or (plain and head_dim % 8 == 0 and head_dim <= 256))):
             # the tensor-core kernels; a block mask or a sink only at the head sizes they are built for

@@ -262,7 +262,7 @@ def test_delta_rule_in_portions(dtype, H, J, d, dv):
         got = []
         for at, q, batch in _state_batches(cuts):
             out = torch.empty(q, H, dv, device=DEV)
-            ops.delta_rule(qkv[at:at + q].contiguous(), offs, beta_src[at:at + q].contiguous(), 1, a_src[at:at + q].contiguous(), 6,
+            ops.delta_rule(qkv[at:at + q].clone(), offs, beta_src[at:at + q].contiguous(), 1, a_src[at:at + q].clone(), 6,      # scratch: overwritten
                            dt_bias, a_log, state, 0, out, batch, H, J, d, dv, d ** -0.5)
             got.append(out)
         outs.append(torch.cat(got))

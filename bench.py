@@ -363,6 +363,33 @@ def step_shares(gf, torch, ops, model, prompts, decode):
     return {k: round(v, 4) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
 
 
+def design_model_bench(a):
+    """One model of the design bench (a config.json given as text): prefill and decode times and kernel shares, one JSON line."""
+    import torch
+    import gpt_fast_b200 as gf
+    from gpt_fast_b200 import ops
+    torch.cuda.set_device(0)
+    label, source = a.design_label, json.loads(a.design_model)
+    lengths = tuple(int(x) for x in a.prefill_lengths.split(","))
+    model = gf.load(source, dtype="bfloat16", device="cuda:0", random_weights=True, seed=0)
+    r = {"weight_gb": round(model.weight_bytes() / 1e9, 3)}
+    r["prefill_ms"] = {}
+    for T in lengths:
+        print(f"[bench] {label}: prefill of {T} tokens", file=sys.stderr, flush=True)
+        r["prefill_ms"][str(T)] = round(prefill_bench(gf, torch, model, T), 3)
+    r["prefill_tok_s"] = {T: round(int(T) / ms * 1e3) for T, ms in r["prefill_ms"].items()}
+    r["decode_ms"], r["decode_tok_s"] = {}, {}
+    for batch in (1, 8, 64):
+        print(f"[bench] {label}: decode, {batch} sequences", file=sys.stderr, flush=True)
+        prompts = random_prompts(torch, model.vocab_size, [512] * batch, 3)
+        ms = decode_bench(gf, torch, model, prompts, 2048, a.steps, a.warmup)[0]
+        r["decode_ms"][str(batch)], r["decode_tok_s"][str(batch)] = round(ms, 4), round(batch / ms * 1e3)
+    r["prefill_shares_ms"] = step_shares(gf, torch, ops, model, random_prompts(torch, model.vocab_size, [min(2048, max(lengths))], 4), False)
+    r["decode_shares_ms"] = step_shares(gf, torch, ops, model, random_prompts(torch, model.vocab_size, [512] * 8, 5), True)
+    print(json.dumps(r))
+    return 0
+
+
 def design_bench(a, design):
     """Prefill and decode throughput of another design of the library at sizes that resemble a real model's layers (random
     weights, bfloat16), beside the Llama decoder at equal size.  One JSON line; the default workload is untouched."""
@@ -390,20 +417,15 @@ def design_bench(a, design):
                 cfg["layers"] = cfg["layers"][:n_layers]
             row = {"size": name, "layers": len(cfg["layers"]), "width": cfg["width"]}
             for label, source in ((design, cfg), (twin_label, twin(cfg))):
-                model = gf.load(source, dtype="bfloat16", device="cuda:0", random_weights=True, seed=0)
-                r = {"weight_gb": round(model.weight_bytes() / 1e9, 3)}
-                r["prefill_ms"] = {str(T): round(prefill_bench(gf, torch, model, T), 3) for T in lengths}
-                r["prefill_tok_s"] = {T: round(int(T) / ms * 1e3) for T, ms in r["prefill_ms"].items()}
-                r["decode_ms"], r["decode_tok_s"] = {}, {}
-                for batch in (1, 8, 64):
-                    prompts = random_prompts(torch, model.vocab_size, [512] * batch, 3)
-                    ms = decode_bench(gf, torch, model, prompts, 2048, a.steps, a.warmup)[0]
-                    r["decode_ms"][str(batch)], r["decode_tok_s"][str(batch)] = round(ms, 4), round(batch / ms * 1e3)
-                r["prefill_shares_ms"] = step_shares(gf, torch, ops, model, random_prompts(torch, model.vocab_size, [min(2048, max(lengths))], 4), False)
-                r["decode_shares_ms"] = step_shares(gf, torch, ops, model, random_prompts(torch, model.vocab_size, [512] * 8, 5), True)
-                row[label] = r
-                del model
-                torch.cuda.empty_cache()
+                # each model in a process of its own: the two then do not share a CUDA context or an allocator
+                cmd = [sys.executable, os.path.abspath(__file__), "--design-model", json.dumps(source), "--design-label", label,
+                       "--steps", str(a.steps), "--warmup", str(a.warmup), "--prefill-lengths", ",".join(str(x) for x in lengths)]
+                proc = subprocess.run(cmd, stdout=subprocess.PIPE, text=True)
+                lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+                if proc.returncode != 0 or not lines:
+                    print(f"bench.py: the run of '{label}' ended with code {proc.returncode}", file=sys.stderr)
+                    return 1
+                row[label] = json.loads(lines[-1])
             out["sizes"].append(row)
     out["clocks"] = clocks.summary()
     print(json.dumps(out))
@@ -433,6 +455,8 @@ def main():
     ap.add_argument("--skip-shares", action="store_true", help="leave out the per-kernel shares")
     ap.add_argument("--design", default=None, help="instead of the default workload: prefill and decode of another design "
                     "(lasezen, gikepel) at layer sizes of a real model, beside the library's closest other model at equal size")
+    ap.add_argument("--design-model", default=None, help=argparse.SUPPRESS)       # one model of --design, run as a child process
+    ap.add_argument("--design-label", default="model", help=argparse.SUPPRESS)
     ap.add_argument("--prefill-lengths", default=None, help="with --design: prompt lengths of the prefill rows (default 512,2048,8192)")
     a = ap.parse_args()
     if a.gpus != 1:
@@ -440,6 +464,8 @@ def main():
         return 2
     if a.impl == "reference":
         return reference_arm(a)
+    if a.design_model:
+        return design_model_bench(a)
     if a.design:
         return design_bench(a, a.design.lower())
 

@@ -129,6 +129,8 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem));
 }
+// a barrier of the two warps that share 16 query rows (named barriers 1..4; 0 is the block's)
+__device__ __forceinline__ void pair_barrier(int pair) { asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory"); }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -290,8 +292,9 @@ GFB_API int gfb_headwise_linear(const void* in, int dt, int ld_in, int in_off, i
 // All heads read the same cached rows: keys are the whole rows (Dk = rank + rot numbers), values their first `rank`
 // numbers.  So the rows of one MMA are (token, head) pairs of ONE sequence, 64 of them per block (four warps of 16),
 // and a tile of 32 cached rows, fetched once into shared memory (cp.async, two stages), serves as the B operand of
-// S = Q K^T (as stored) and of O += P V (transposed on the way into the registers).  The value columns are split
-// between two warps per 16 query rows (each computes the same scores and keeps half of O in registers: 128 numbers
+// S = Q K^T (as stored) and of O += P V (transposed on the way into the registers).  Two warps share 16 query rows:
+// each scores half of the tile's keys, they agree on the rows' maxima and exchange their softmax weights through shared
+// memory (two barriers of 64 threads per tile), and each keeps half of the value columns of O in registers (128 numbers
 // per thread at rank 512).  bfloat16 operands on `mma.sync.m16n8k16`, scores, softmax and sums in 32-bit; the softmax
 // weights are rounded to bfloat16 for the second product.  Keys are masked per row by the row's own position.
 constexpr int LA_ROWS = 64;           // query rows per block
@@ -308,6 +311,8 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
     const int DkP = Dk + LA_PAD;
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [LA_ROWS][DkP]
     __nv_bfloat16* sK = sQ + (size_t)LA_ROWS * DkP;                             // [2][LA_KEYS][DkP]
+    __shared__ __align__(16) __nv_bfloat16 sP[4][16][LA_KEYS + LA_PAD];         // a warp pair's softmax weights of the tile
+    __shared__ float sMax[4][2][16], sSum[4][2][16];                            // each half's row maxima of the tile; row sums at the end
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int s = blockIdx.x;
@@ -352,8 +357,8 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
         *reinterpret_cast<uint4*>(sQ + (size_t)r * DkP + cc * 8) = v;
     }
 
-    const int rw = (warp & 3) * 16;                    // the warp's 16 query rows
-    const int half = warp >> 2;                        // which half of the value columns it keeps
+    const int pair = warp & 3, rw = pair * 16;         // the warp's 16 query rows, shared with the warp `pair + 4`
+    const int half = warp >> 2;                        // which half of a tile's keys it scores and of the value columns it keeps
     const int nt_all = R / 8, nt_lo = half == 0 ? 0 : (nt_all + 1) / 2, nt_n = half == 0 ? (nt_all + 1) / 2 : nt_all - (nt_all + 1) / 2;
     const int r0 = rw + (lane >> 2);                   // rows of this thread's accumulator values: r0 and r0 + 8
     const int pos0 = (r0 < rows_here) ? start + (m0 + r0) / H : -1, pos1 = (r0 + 8 < rows_here) ? start + (m0 + r0 + 8) / H : -1;
@@ -373,26 +378,22 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
         }
         __syncthreads();
         const __nv_bfloat16* kt = sK + (size_t)stage * LA_KEYS * DkP;
-        // scores of 16 rows x 32 keys
-        float sc[LA_KEYS / 8][4];
+        // scores of 16 rows x 16 keys: the two warps of a pair take half of the tile's keys each
+        float sc[2][4];
 #pragma unroll
-        for (int j = 0; j < LA_KEYS / 8; j++) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+        for (int j = 0; j < 2; j++) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
         for (int kk = 0; kk < Dk; kk += 16) {
-            uint32_t a[4];
+            uint32_t a[4], bb[4];
             ldsm_x4(a, sQ + (size_t)(rw + (lane & 7) + 8 * ((lane >> 3) & 1)) * DkP + kk + 8 * (lane >> 4));
-#pragma unroll
-            for (int j = 0; j < LA_KEYS / 8; j += 2) {
-                uint32_t bb[4];
-                ldsm_x4(bb, kt + (size_t)((j + (lane >> 4)) * 8 + (lane & 7)) * DkP + kk + 8 * ((lane >> 3) & 1));
-                mma_bf16(sc[j], a, bb[0], bb[1]);
-                mma_bf16(sc[j + 1], a, bb[2], bb[3]);
-            }
+            ldsm_x4(bb, kt + (size_t)((2 * half + (lane >> 4)) * 8 + (lane & 7)) * DkP + kk + 8 * ((lane >> 3) & 1));
+            mma_bf16(sc[0], a, bb[0], bb[1]);
+            mma_bf16(sc[1], a, bb[2], bb[3]);
         }
-        // mask by each row's position, running maximum and sum
-        const int key0 = tile * LA_KEYS + 2 * (lane & 3);
+        // mask by each row's position; the pair agrees on the rows' maxima through shared memory
+        const int key0 = tile * LA_KEYS + 16 * half + 2 * (lane & 3);
         float t0m = -INFINITY, t1m = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < LA_KEYS / 8; j++) {
+        for (int j = 0; j < 2; j++) {
 #pragma unroll
             for (int e = 0; e < 2; e++) {
                 const int key = key0 + j * 8 + e;
@@ -406,21 +407,29 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
         t0m = fmaxf(t0m, __shfl_xor_sync(0xffffffffu, t0m, 2));
         t1m = fmaxf(t1m, __shfl_xor_sync(0xffffffffu, t1m, 1));
         t1m = fmaxf(t1m, __shfl_xor_sync(0xffffffffu, t1m, 2));
+        if ((lane & 3) == 0) { sMax[pair][half][lane >> 2] = t0m; sMax[pair][half][(lane >> 2) + 8] = t1m; }
+        pair_barrier(pair);
+        t0m = fmaxf(t0m, sMax[pair][half ^ 1][lane >> 2]);
+        t1m = fmaxf(t1m, sMax[pair][half ^ 1][(lane >> 2) + 8]);
         const float n0 = fmaxf(mx0, t0m), n1 = fmaxf(mx1, t1m);
         const float u0 = n0 == -INFINITY ? 0.f : n0, u1 = n1 == -INFINITY ? 0.f : n1;       // a row that sees nothing yet
         const float al0 = exp2f(mx0 - u0), al1 = exp2f(mx1 - u1);                             // exp2(-inf) = 0
         mx0 = n0;
         mx1 = n1;
-        float s0 = 0.f, s1 = 0.f;
-        uint32_t pa[LA_KEYS / 16][4];
+        float s0 = 0.f, s1 = 0.f;                       // sums over this warp's keys only; the halves are added at the end
 #pragma unroll
-        for (int j = 0; j < LA_KEYS / 8; j++) {
+        for (int j = 0; j < 2; j++) {
             const float p00 = exp2f(sc[j][0] - u0), p01 = exp2f(sc[j][1] - u0), p10 = exp2f(sc[j][2] - u1), p11 = exp2f(sc[j][3] - u1);
             s0 += p00 + p01;
             s1 += p10 + p11;
-            pa[j >> 1][(j & 1) * 2] = pack_bf16(p00, p01);
-            pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p10, p11);
+            const int col = 16 * half + 8 * j + 2 * (lane & 3);
+            *reinterpret_cast<uint32_t*>(&sP[pair][lane >> 2][col]) = pack_bf16(p00, p01);
+            *reinterpret_cast<uint32_t*>(&sP[pair][(lane >> 2) + 8][col]) = pack_bf16(p10, p11);
         }
+        pair_barrier(pair);
+        uint32_t pa[LA_KEYS / 16][4];
+#pragma unroll
+        for (int kb = 0; kb < LA_KEYS / 16; kb++) ldsm_x4(pa[kb], &sP[pair][(lane & 7) + 8 * ((lane >> 3) & 1)][kb * 16 + 8 * (lane >> 4)]);
         s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
         s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
         s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
@@ -448,6 +457,11 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
         }
         __syncthreads();                               // the stage is free for the tile after next
     }
+    // the row sums of the two halves (both under the same maxima)
+    if ((lane & 3) == 0) { sSum[pair][half][lane >> 2] = l0; sSum[pair][half][(lane >> 2) + 8] = l1; }
+    pair_barrier(pair);
+    l0 += sSum[pair][half ^ 1][lane >> 2];
+    l1 += sSum[pair][half ^ 1][(lane >> 2) + 8];
     if (n_splits > 1) {
         // [row][split][R values, maximum (base-2 exponent), sum]
         float* base = partial + (((size_t)t0 * H + m0) * n_splits + blockIdx.z) * (R + 2);

@@ -114,7 +114,7 @@ GFB_API int gfb_short_conv(const void* src, int dt, int ld, int col_off, int C, 
 // the sequence's tokens of this step.  The rows are dealt in groups of RPT to RG lanes of a warp (RG a power of two),
 // a warp holds 32 / RG columns, a block four warps.  A sum over the rows is RPT terms per lane in ascending order and
 // then a butterfly over the RG lanes: no barrier per token.  The inputs of TB tokens are staged in shared memory at a
-// time (row vectors padded by one number per group so that the RG lanes read distinct banks), in two stages: the next
+// time (row vectors padded per group so that the RG lanes read distinct banks with 16-byte loads), in two stages: the next
 // tile's copies (cp.async) run under the current tile's steps.
 constexpr int TB = 16;
 constexpr int SCAN_WARPS = 4;
@@ -123,7 +123,18 @@ __device__ __forceinline__ float group_sum(float v, int RG) {
     for (int o = RG >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
-__device__ __forceinline__ int padded(int c, int RPT) { return c + c / RPT; }      // index of row c in a padded row vector
+constexpr int ROW_PAD = 4;            // numbers of padding per group of RPT rows: 16-byte loads of a group stay aligned and
+                                      // the lanes of a column fall into distinct banks
+__device__ __forceinline__ int padded(int c, int RPT) { return c + (c / RPT) * ROW_PAD; }      // index of row c in a padded row vector
+// RPT consecutive numbers of shared memory into registers, four at a time
+template <int RPT>
+__device__ __forceinline__ void load_rows(float (&r)[RPT], const float* p) {
+#pragma unroll
+    for (int i = 0; i < RPT; i += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(p + i);
+        r[i] = v.x; r[i + 1] = v.y; r[i + 2] = v.z; r[i + 3] = v.w;
+    }
+}
 // One 32-bit number from global to shared memory without passing a register: a tile's copies are all in flight at once
 // and the next tile's run under the current tile's steps.
 __device__ __forceinline__ void copy_async4(float* smem, const float* gmem) {
@@ -141,11 +152,11 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
                 int dt_off, const void* __restrict__ dt_bias, const void* __restrict__ a_log, const void* __restrict__ skip,
                 int w_dt, float* __restrict__ state, size_t state_ld, float* __restrict__ out, GfbBatch b, int H, int P, int N,
                 int G, int RG) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int s = blockIdx.x, h = blockIdx.y, g = h / (H / G);
-    const int CW = 32 / RG, CB = SCAN_WARPS * CW, NP = RG * (RPT + 1);
+    const int CW = 32 / RG, CB = SCAN_WARPS * CW, NP = RG * (RPT + ROW_PAD);
     const int STAGE = TB * (2 * NP + CB + 2);
     float* sO = sm + 2 * STAGE;           // [TB][CB]; ahead of it two stages of: B [TB][NP], C [TB][NP], x [TB][CB], dt [TB], decay [TB]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -209,8 +220,9 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
         __syncthreads();                                       // this tile's inputs have landed; the previous outputs are written
         for (int tt = 0; tt < nt; tt++) {
             const float a = sA[tt], dx = sDt[tt], xp = sX[tt * CB + cl];
-            const float* bb = sB + tt * NP + rgi * (RPT + 1);
-            const float* cc = sC + tt * NP + rgi * (RPT + 1);
+            float bb[RPT], cc[RPT];
+            load_rows<RPT>(bb, sB + tt * NP + rgi * (RPT + ROW_PAD));
+            load_rows<RPT>(cc, sC + tt * NP + rgi * (RPT + ROW_PAD));
             float acc = 0.f;
 #pragma unroll
             for (int r = 0; r < RPT; r++) {
@@ -267,11 +279,11 @@ __global__ void __launch_bounds__(32 * SCAN_WARPS)
 delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, int v_off, const TD* __restrict__ beta_raw, int ld_b,
                   int beta_off, const float* __restrict__ decay, int ld_a, int a_off, float* __restrict__ state, size_t state_ld,
                   float* __restrict__ out, GfbBatch b, int H, int KH, int d, int dv, int RG) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int s = blockIdx.x, h = blockIdx.y, kh = h / (H / KH);
-    const int CW = 32 / RG, CB = SCAN_WARPS * CW, NP = RG * (RPT + 1);
+    const int CW = 32 / RG, CB = SCAN_WARPS * CW, NP = RG * (RPT + ROW_PAD);
     const int STAGE = TB * (3 * NP + CB + 1);
     float* sO = sm + 2 * STAGE;           // [TB][CB]; ahead of it two stages of: q, k, decay [TB][NP] each, v [TB][CB], beta [TB]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -332,14 +344,13 @@ delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, 
         }
         __syncthreads();                                       // this tile's inputs have landed; the previous outputs are written
         for (int tt = 0; tt < nt; tt++) {
-            const float* gg = sG + tt * NP + rgi * (RPT + 1);
-            const float* kk = sK + tt * NP + rgi * (RPT + 1);
-            const float* qq = sQ + tt * NP + rgi * (RPT + 1);
-            float kr[RPT];
+            float gg[RPT], kr[RPT], qq[RPT];
+            load_rows<RPT>(gg, sG + tt * NP + rgi * (RPT + ROW_PAD));
+            load_rows<RPT>(kr, sK + tt * NP + rgi * (RPT + ROW_PAD));
+            load_rows<RPT>(qq, sQ + tt * NP + rgi * (RPT + ROW_PAD));
             float acc = 0.f;
 #pragma unroll
             for (int r = 0; r < RPT; r++) {
-                kr[r] = kk[r];
                 st[r] *= gg[r];
                 acc = fmaf(st[r], kr[r], acc);
             }
@@ -410,7 +421,7 @@ GFB_API int gfb_ssd_scan(const float* x, int ldx, int b_off, int c_off, const vo
     const int CB = SCAN_WARPS * (32 / RG);
     const unsigned slices = (unsigned)((P + CB - 1) / CB);
     if (H > 65535 || slices > 65535) return gfb_fail("gfb_ssd_scan: %d heads of %d columns exceed the grid limit", H, P);
-    const size_t smem = ((size_t)2 * TB * (2 * RG * (rpt + 1) + CB + 2) + (size_t)TB * CB) * sizeof(float);
+    const size_t smem = ((size_t)2 * TB * (2 * RG * (rpt + ROW_PAD) + CB + 2) + (size_t)TB * CB) * sizeof(float);
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     cudaError_t e = cudaSuccess;
 #define GO(TD, R)                                                                                                          \
@@ -443,7 +454,7 @@ GFB_API int gfb_delta_rule(float* qkv, int ldq, int q_off, int k_off, int v_off,
     const int CB = SCAN_WARPS * (32 / RG);
     const unsigned slices = (unsigned)((dv + CB - 1) / CB);
     if (H > 65535 || slices > 65535) return gfb_fail("gfb_delta_rule: %d heads of %d columns exceed the grid limit", H, dv);
-    const size_t smem = ((size_t)2 * TB * (3 * RG * (rpt + 1) + CB + 1) + (size_t)TB * CB) * sizeof(float);
+    const size_t smem = ((size_t)2 * TB * (3 * RG * (rpt + ROW_PAD) + CB + 1) + (size_t)TB * CB) * sizeof(float);
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     cudaError_t e = gfb_launch(delta_prepare_kernel, dim3(n_tokens), dim3(128), 0, stream, qkv, ldq, q_off, k_off, a_raw, ld_a, a_off,
                                dt_bias, a_log, w_dt, H, KH, d, q_scale, unit_eps);

@@ -113,7 +113,9 @@ GFB_API int gfb_short_conv(const void* src, int dt, int ld, int col_off, int C, 
 // columns evolve independently, so a block takes one (sequence, head) and a slice of the columns and walks through
 // the sequence's tokens of this step.  The rows are dealt in groups of RPT to RG lanes of a warp (RG a power of two),
 // a warp holds 32 / RG columns, a block four warps.  A sum over the rows is RPT terms per lane in ascending order and
-// then a butterfly over the RG lanes: no barrier per token.  The inputs of TB tokens are staged in shared memory at a
+// then either a butterfly over the RG lanes (the delta rule's S^T k, which the token's own update waits for) or, for the
+// outputs, which nothing waits for, the lanes' parts left in shared memory and added in ascending order behind the
+// tile's steps: no barrier per token.  The inputs of TB tokens are staged in shared memory at a
 // time (row vectors padded per group so that the RG lanes read distinct banks with 16-byte loads), in two stages: the next
 // tile's copies (cp.async) run under the current tile's steps.
 constexpr int TB = 16;
@@ -125,6 +127,12 @@ __device__ __forceinline__ float group_sum(float v, int RG) {
 }
 constexpr int ROW_PAD = 4;            // numbers of padding per group of RPT rows: 16-byte loads of a group stay aligned and
                                       // the lanes of a column fall into distinct banks
+// the lanes' parts of a column's sum, in ascending order
+__device__ __forceinline__ float sum_parts(const float* part, int RG) {
+    float v = part[0];
+    for (int r = 1; r < RG; r++) v += part[r];
+    return v;
+}
 __device__ __forceinline__ int padded(int c, int RPT) { return c + (c / RPT) * ROW_PAD; }      // index of row c in a padded row vector
 // RPT consecutive numbers of shared memory into registers, four at a time
 template <int RPT>
@@ -141,6 +149,11 @@ __device__ __forceinline__ void copy_async4(float* smem, const float* gmem) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(gmem));
 }
+__device__ __forceinline__ void copy_async16(float* smem, const float* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem));
+}
+__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 __device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
@@ -183,14 +196,22 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
     }
     __syncthreads();
     float dt_next = 0.f;
+    const bool wide = N % 4 == 0 && ldx % 4 == 0 && aligned16(x + b_off + g * N) && aligned16(x + c_off + g * N);
     auto fetch = [&](int stage, int tile) {
         float* base = sm + stage * STAGE;
         const int nt = min(TB, t1 - tile);
         for (int tt = warp; tt < nt; tt += SCAN_WARPS) {
             const float* row = x + (size_t)(tile + tt) * ldx;
-            for (int n = lane; n < N; n += 32) {
-                copy_async4(base + tt * NP + padded(n, RPT), row + b_off + g * N + n);
-                copy_async4(base + TB * NP + tt * NP + padded(n, RPT), row + c_off + g * N + n);
+            if (wide) {                                            // four numbers per copy (a group of RPT rows is contiguous)
+                for (int n = 4 * lane; n < N; n += 128) {
+                    copy_async16(base + tt * NP + padded(n, RPT), row + b_off + g * N + n);
+                    copy_async16(base + TB * NP + tt * NP + padded(n, RPT), row + c_off + g * N + n);
+                }
+            } else {
+                for (int n = lane; n < N; n += 32) {
+                    copy_async4(base + tt * NP + padded(n, RPT), row + b_off + g * N + n);
+                    copy_async4(base + TB * NP + tt * NP + padded(n, RPT), row + c_off + g * N + n);
+                }
             }
             for (int q = lane; q < CB && p0 + q < P; q += 32) copy_async4(base + 2 * TB * NP + tt * CB + q, row + (size_t)h * P + p0 + q);
         }
@@ -229,8 +250,8 @@ ssd_scan_kernel(const float* __restrict__ x, int ldx, int b_off, int c_off, cons
                 st[r] = fmaf(a, st[r], (dx * bb[r]) * xp);
                 acc = fmaf(st[r], cc[r], acc);
             }
-            acc = group_sum(acc, RG);
-            if (rgi == 0) sO[tt * CB + cl] = acc + dskip * xp;
+            acc = group_sum(acc, RG);                // (leaving the lanes' parts in shared memory as the delta rule does costs a
+            if (rgi == 0) sO[tt * CB + cl] = acc + dskip * xp;      //  fourth block per SM its room, and with it a second round of blocks)
         }
         __syncthreads();
         for (int tt = warp; tt < nt; tt += SCAN_WARPS)
@@ -285,7 +306,7 @@ delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, 
     const int s = blockIdx.x, h = blockIdx.y, kh = h / (H / KH);
     const int CW = 32 / RG, CB = SCAN_WARPS * CW, NP = RG * (RPT + ROW_PAD);
     const int STAGE = TB * (3 * NP + CB + 1);
-    float* sO = sm + 2 * STAGE;           // [TB][CB]; ahead of it two stages of: q, k, decay [TB][NP] each, v [TB][CB], beta [TB]
+    float* sO = sm + 2 * STAGE;           // [TB][CB][RG] the lanes' parts of the outputs; ahead of it two stages of: q, k, decay [TB][NP] each, v [TB][CB], beta [TB]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int rgi = lane % RG, cl = warp * CW + lane / RG;
     const int p0 = blockIdx.z * CB, p = p0 + cl;
@@ -309,17 +330,28 @@ delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, 
     }
     __syncthreads();
     float beta_next = 0.f;
+    const bool wide = d % 4 == 0 && ldq % 4 == 0 && ld_a % 4 == 0 && aligned16(qkv + q_off + kh * d) && aligned16(qkv + k_off + kh * d) &&
+                      aligned16(decay + a_off + (size_t)h * d);
     auto fetch = [&](int stage, int tile) {
         float* base = sm + stage * STAGE;
         const int nt = min(TB, t1 - tile);
         for (int tt = warp; tt < nt; tt += SCAN_WARPS) {
             const float* row = qkv + (size_t)(tile + tt) * ldq;
             const float* grow = decay + (size_t)(tile + tt) * ld_a + a_off + (size_t)h * d;
-            for (int c = lane; c < d; c += 32) {
-                const int at = tt * NP + padded(c, RPT);
-                copy_async4(base + at, row + q_off + kh * d + c);
-                copy_async4(base + TB * NP + at, row + k_off + kh * d + c);
-                copy_async4(base + 2 * TB * NP + at, grow + c);
+            if (wide) {                                            // four numbers per copy (a group of RPT rows is contiguous)
+                for (int c = 4 * lane; c < d; c += 128) {
+                    const int at = tt * NP + padded(c, RPT);
+                    copy_async16(base + at, row + q_off + kh * d + c);
+                    copy_async16(base + TB * NP + at, row + k_off + kh * d + c);
+                    copy_async16(base + 2 * TB * NP + at, grow + c);
+                }
+            } else {
+                for (int c = lane; c < d; c += 32) {
+                    const int at = tt * NP + padded(c, RPT);
+                    copy_async4(base + at, row + q_off + kh * d + c);
+                    copy_async4(base + TB * NP + at, row + k_off + kh * d + c);
+                    copy_async4(base + 2 * TB * NP + at, grow + c);
+                }
             }
             for (int c = lane; c < CB && p0 + c < dv; c += 32) copy_async4(base + 3 * TB * NP + tt * CB + c, row + v_off + (size_t)h * dv + p0 + c);
         }
@@ -362,13 +394,13 @@ delta_rule_kernel(const float* __restrict__ qkv, int ldq, int q_off, int k_off, 
                 st[r] = fmaf(kr[r], u, st[r]);
                 o = fmaf(st[r], qq[r], o);
             }
-            o = group_sum(o, RG);
-            if (rgi == 0) sO[tt * CB + cl] = o;
+            // nothing of the next token waits for this sum: the lanes leave their parts, added behind the tile's steps
+            sO[(tt * CB + cl) * RG + rgi] = o;
         }
         __syncthreads();
         for (int tt = warp; tt < nt; tt += SCAN_WARPS)
             for (int c = lane; c < CB; c += 32)
-                if (p0 + c < dv) out[(size_t)(tile + tt) * H * dv + (size_t)h * dv + p0 + c] = sO[tt * CB + c];
+                if (p0 + c < dv) out[(size_t)(tile + tt) * H * dv + (size_t)h * dv + p0 + c] = sum_parts(sO + (tt * CB + c) * RG, RG);
     }
     if (active) {
 #pragma unroll
@@ -454,7 +486,7 @@ GFB_API int gfb_delta_rule(float* qkv, int ldq, int q_off, int k_off, int v_off,
     const int CB = SCAN_WARPS * (32 / RG);
     const unsigned slices = (unsigned)((dv + CB - 1) / CB);
     if (H > 65535 || slices > 65535) return gfb_fail("gfb_delta_rule: %d heads of %d columns exceed the grid limit", H, dv);
-    const size_t smem = ((size_t)2 * TB * (3 * RG * (rpt + ROW_PAD) + CB + 1) + (size_t)TB * CB) * sizeof(float);
+    const size_t smem = ((size_t)2 * TB * (3 * RG * (rpt + ROW_PAD) + CB + 1) + (size_t)TB * CB * RG) * sizeof(float);
     GfbBatch b{cu_seqlens, tok_seq, slots, lengths, n_seqs, n_tokens};
     cudaError_t e = gfb_launch(delta_prepare_kernel, dim3(n_tokens), dim3(128), 0, stream, qkv, ldq, q_off, k_off, a_raw, ld_a, a_off,
                                dt_bias, a_log, w_dt, H, KH, d, q_scale, unit_eps);

@@ -10,7 +10,6 @@ the kind of part that fills it ('mixer', 'feed_forward', 'norm': the registries 
 and hands them over as a dict; mixers also receive the layer's position encoding."""
 import torch
 
-from .. import ops
 from ..weights.loader import ParamSpec
 from . import register_block
 from .residual import Branch, as_residual

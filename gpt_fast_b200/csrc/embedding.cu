@@ -13,7 +13,7 @@ GFB_DEFINE_LAST_ERROR()
 template <typename TW>
 __global__ void embed_hashed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, const TW* __restrict__ extra,
                                     float* __restrict__ out, GfbBatch b, const int* __restrict__ prev, int D, int V,
-                                    int buckets, int mul_prev, int mul_cur, float scale, int* status) {
+                                    int buckets, long long mul_prev, long long mul_cur, float scale, int* status) {
     gfb_pdl_launch();
     gfb_pdl_wait();
     const int t = blockIdx.x;
@@ -31,7 +31,7 @@ __global__ void embed_hashed_kernel(const int* __restrict__ tokens, const TW* __
     if (t > b.cu_seqlens[s]) before = tokens[t - 1];
     else if (b.lengths[slot] > 0) before = prev[slot];
     if (before >= 0) {
-        row = ((long long)before * mul_prev + (long long)id * mul_cur) % buckets;
+        row = ((long long)before * mul_prev + (long long)id * mul_cur) % buckets;      // 64-bit: the multipliers may be large
         if (row < 0) row += buckets;
     }
     const TW* e = table + (size_t)id * D;
@@ -51,7 +51,7 @@ __global__ void embed_prev_kernel(const int* __restrict__ tokens, GfbBatch b, in
 // tokens int32 [T]; table [V, D] and extra [buckets + 1, D] of type table_dt; out float32 [T, D]; prev int32 [n_slots].
 GFB_API int gfb_embed_hashed(const int* tokens, const void* table, const void* extra, int table_dt, float* out,
                              const int* cu_seqlens, const int* tok_seq, const int* slots, const int* lengths, int n_seqs,
-                             int n_tokens, int* prev, int D, int V, int buckets, int mul_prev, int mul_cur, float scale,
+                             int n_tokens, int* prev, int D, int V, int buckets, long long mul_prev, long long mul_cur, float scale,
                              int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (buckets <= 0) return gfb_fail("gfb_embed_hashed: %d buckets", buckets);

@@ -1,7 +1,7 @@
 """ctypes bindings of the kernel libraries: host-side checks, kernel choice,
 launch on the current stream."""
 import ctypes
-from ctypes import c_float, c_int, c_long, c_ulonglong, c_void_p
+from ctypes import c_float, c_int, c_long, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
 
 import torch
@@ -126,7 +126,7 @@ class CudaKernels:
         _need(out, torch.float32, (T, D), "embedding output")
         _need(prev, torch.int32, name="previous tokens")
         self._call("embedding", "gfb_embed_hashed", _ptr(tokens), _ptr(table), _ptr(extra), c_int(_dt(table)), _ptr(out),
-                   *self._batch_args(batch), _ptr(prev), c_int(D), c_int(V), c_int(buckets), c_int(mul_prev), c_int(mul_cur),
+                   *self._batch_args(batch), _ptr(prev), c_int(D), c_int(V), c_int(buckets), c_longlong(mul_prev), c_longlong(mul_cur),
                    c_float(scale), _ptr(batch.status), _stream())
 
     def softcap(self, x, cap):

@@ -31,7 +31,7 @@ def cpu_batch(batch):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_embed_hashed_whole_and_in_portions(dtype):
-    V, D, buckets, mp, mc = 300, 56, 37, 1031, 7
+    V, D, buckets, mp, mc = 300, 56, 37, 3_000_000_019, 7        # a multiplier beyond 32 bits
     table, extra = rnd(V, D, dtype=dtype, seed=1), rnd(buckets + 1, D, dtype=dtype, seed=2)
     toks = torch.randint(0, V, (23,), generator=torch.Generator().manual_seed(3)).tolist()
     want = pg.embedding(toks, d64(table), d64(extra), buckets, mp, mc)

@@ -299,3 +299,40 @@ def test_trace_run(folders, tmp_path, dtype):
                 outputs[s["step"]] = np.fromfile(os.path.join(out_dir, f"{s['step']}.f32"), dtype="<f4").reshape(wanted, V)
         for (rid, j), row in traces.collect(steps, outputs, V).items():
             judge(torch.from_numpy(row.copy())[None], folder, reqs[rid], slice(j, j + 1), dtype, f"{cut}: {rid}[{j}]")
+
+
+# ---- long decoding: the states carry over hundreds of steps ------------------------------------------------------
+
+def test_long_decoding(folders, backend):
+    name = NAMES[0]
+    model, cache, st = make(folders[name], backend)
+    toks = tokens_of(model.vocab_size, 330, seed=9)
+    (slot,) = cache.begin(1)
+    got = stepped(st, slot, toks, [5] + list(range(6, len(toks))))
+    cache.end([slot])
+    judge(got[-40:], folders[name], toks, slice(len(toks) - 40, len(toks)), backend[1], f"{name}: the last of 325 decode steps")
+
+
+# ---- the command line as a user runs it ----------------------------------------------------------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cli_greedy(folders, tmp_path, dtype):
+    from test_cli_gpu import read_lines, run_cli
+    name = NAMES[1]
+    out = tmp_path / "tokens.jsonl"
+    r = run_cli("--checkpoint_path", folders[name], "--prompt", "4,13", "--max_new_tokens", "7", "--temperature", "0",
+                "--dtype", dtype, "--output", str(out))
+    assert r.returncode == 0, r.stderr[-2000:]
+    rows = read_lines(out)
+    assert [len(x["prompt"]) for x in rows] == [4, 13]
+    for x in rows:
+        assert len(x["tokens"]) == 7
+        seq = list(x["prompt"])
+        for tok in x["tokens"]:
+            logits = plain(folders[name], seq)[-1]
+            margin = 1e-3 if dtype == "float32" else 0.05 * float(logits.pow(2).mean().sqrt()) + 0.05
+            if tok != int(torch.argmax(logits)):
+                assert logits[tok] >= logits.max() - margin, f"request {x['request']}: chose {tok}"
+                break                                          # a near tie turned the other way: the sequences part here
+            seq.append(tok)

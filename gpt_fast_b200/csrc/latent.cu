@@ -317,7 +317,8 @@ latent_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
     gfb_pdl_wait();
     const int s = blockIdx.x;
     const int t0 = b.cu_seqlens[s], n_rows = (b.cu_seqlens[s + 1] - t0) * H;
-    const int m0 = blockIdx.y * LA_ROWS;
+    // the latest rows see the most keys: they come first, so that the blocks of the last round are the short ones
+    const int m0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * LA_ROWS;
     if (m0 >= n_rows) return;
     const int slot = b.slots[s], start = b.lengths[slot];
     const int rows_here = min(LA_ROWS, n_rows - m0);

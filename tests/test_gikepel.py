@@ -336,3 +336,27 @@ def test_cli_greedy(folders, tmp_path, dtype):
                 assert logits[tok] >= logits.max() - margin, f"request {x['request']}: chose {tok}"
                 break                                          # a near tie turned the other way: the sequences part here
             seq.append(tok)
+
+
+# ---- other orders of layers, widths that no 16-byte kernel takes ----------------------------------------------------
+
+@pytest.mark.parametrize("which", ["no-attention", "only-attention", "one-layer", "one-tap"])
+def test_other_layer_orders(tmp_path, backend, which):
+    """Models without any cached keys, without any recurrent state, of one layer, with convolutions of one tap; width 52 and
+    vocabulary 97, so that the bfloat16 products take the kernels for rows that are no whole 16-byte units."""
+    device, dtype = backend
+    base = gf.config_from_name(NAMES[0])
+    L = base["layers"]
+    layers = {"no-attention": [L[0], L[2], L[0]], "only-attention": [L[1], L[1]], "one-layer": [L[2]],
+              "one-tap": [dict(L[0], mixer=dict(L[0]["mixer"], conv=1)), dict(L[2], mixer=dict(L[2]["mixer"], conv=1))]}[which]
+    cfg = dict(base, layers=json.loads(json.dumps(layers)), width=52, vocab=97)
+    folder = str(tmp_path / which)
+    gf.write_model_folder(folder, cfg, seed=3, std=0.11, jitter=0.2)
+    model = gf.load(folder, dtype=dtype, device=device)
+    cache = model.new_cache(max_tokens=256, max_seqs=2)
+    st = Stepper(model, cache)
+    toks = tokens_of(97, 70, seed=8)
+    (slot,) = cache.begin(1)
+    got = stepped(st, slot, toks, [33, 34])
+    cache.end([slot])
+    judge(got, folder, toks, slice(None), dtype, which)
